@@ -414,3 +414,57 @@ class MLAAttention:
                                              seq_state.kv_indices(hidden.device).data_ptr(), seq_state.seq_len + M,
                                              out.data_ptr(), M, _stream(hidden.device)))
         return out
+
+
+# ------------------------------------------------------------------------------------------------ caches of ragged-batch serving
+
+class LatentKVCache(PagedKVCache):
+    """Paged cache of latent attention for several live sequences: per attention layer one pool of latents
+    [max_pages, page_size, kv_rank] and one of shared rotated keys [max_pages, page_size, rot_dim], in the serving dtype (bfloat16
+    or float32, not FP8: a step's logits may not depend on how a prompt was cut).  Layers may differ in their sizes; all of them
+    share one page numbering, so a sequence holds one page list (`SequenceKVState`) whatever the number of layers.
+    Allocation is the free list of `PagedKVCache`; pages go back with `SequenceKVState.free()` and are handed out again."""
+
+    def __init__(self, layer_dims, device, max_pages: int, dtype=torch.bfloat16, page_size: int = 64):
+        if dtype not in (torch.bfloat16, torch.float32):
+            raise ValueError("latent cache dtype: bfloat16 or float32")
+        self.num_layers, self.page_size, self.kv_dtype, self.max_pages = len(layer_dims), page_size, dtype, max_pages
+        self.device = torch.device(device)
+        self.ckv = [torch.zeros((max_pages, page_size, r), dtype=dtype, device=self.device) for r, _ in layer_dims]
+        self.kr = [torch.zeros((max_pages, page_size, max(d, 1)), dtype=dtype, device=self.device) for _, d in layer_dims]
+        self._free = list(range(max_pages - 1, -1, -1))
+
+    def get_layer_caches(self, layer_offset: int):
+        return self.ckv[layer_offset], self.kr[layer_offset]
+
+
+class RecurrentStatePool:
+    """State slots of recurrent mixers for several live sequences.  A slot is one index into every registered tensor
+    ([slots, ...] fp32, one per recurrent layer run); `alloc()` hands out a zeroed slot, `free()` returns it for reuse."""
+
+    def __init__(self, num_slots: int, device):
+        self.num_slots, self.device = num_slots, torch.device(device)
+        self.tensors = []
+        self._free = list(range(num_slots - 1, -1, -1))
+
+    def register(self, *shape) -> torch.Tensor:
+        t = torch.zeros((self.num_slots,) + tuple(shape), dtype=torch.float32, device=self.device)
+        self.tensors.append(t)
+        return t
+
+    @property
+    def free_slot_count(self) -> int:
+        return len(self._free)
+
+    def alloc(self) -> int:
+        if not self._free:
+            raise RuntimeError("no free state slot")
+        slot = self._free.pop()
+        for t in self.tensors:
+            t[slot].zero_()
+        return slot
+
+    def free(self, slot: int):
+        if slot in self._free or not 0 <= slot < self.num_slots:
+            raise ValueError(f"slot {slot} is not in use")
+        self._free.append(slot)

@@ -1,0 +1,709 @@
+// Ragged-batch sequence operators: the kernels a decoder needs when one step carries portions of several prompts next to single
+// decoded tokens.  Every kernel works on a flat token axis [T] with per-token (sequence, position) and per-sequence
+// (first row, state slot, page list) metadata, so prefill, chunked prefill, decode and any mixture run the same code.
+//
+//   embed_scale            x = table[token] * scale                                   (fp32 residual stream)
+//   gemm_nt / gemv_nt      C = A B^T for any M, N, K; fp32 or bf16 operands, fp32 accumulation in a fixed K order per output
+//   residual_norm          x += norm(y) (+ x0);  h = layer_norm(x)                    (residual update fused with the next norm)
+//   act_mul                gelu_tanh(a) * b                                           (gated feed-forward)
+//   side_gate              gelu_tanh(g) * per-layer slice of a token table            (per-layer token input)
+//   latent_prep            RMS-normed latent + rotated shared key -> paged cache, rotary on the query's rotated part (YaRN table)
+//   latent_window_attn     absorbed-form latent attention over the page list: sliding window, softmax with a per-head sink
+//   conv_silu (+ state)    short causal convolution per channel over time with a carried tail, then SiLU
+//   delta_rule             gated delta rule S <- g S; u = beta (v - S^T k); S += k u^T; o = S^T q, state in fp32 slots,
+//                          unit-norm q / k, per-head RMS norm of o with a SiLU gate
+//
+// Precision: the residual stream, every norm, softmax, the rotary angles, decays, gates and the recurrent state are fp32 (angles
+// are reduced in fp64).  `dt` codes: 0 = float32, 1 = bfloat16.
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <math.h>
+#include <stdarg.h>
+#include <stdint.h>
+#include <stdio.h>
+
+#include "../../include/krasis_b200_seq.h"
+
+namespace kb2seq {
+
+typedef __nv_bfloat16 bf16;
+
+static thread_local char g_err[512] = "";
+static long long g_launches = 0;
+
+static int failf(int code, const char* fmt, ...) {
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(g_err, sizeof(g_err), fmt, ap);
+  va_end(ap);
+  return code;
+}
+
+#define SEQ_CUDA(expr)                                                                              \
+  do {                                                                                              \
+    cudaError_t _e = (expr);                                                                        \
+    if (_e != cudaSuccess) return failf(KB2SEQ_ERR_CUDA, "%s: %s", #expr, cudaGetErrorString(_e)); \
+  } while (0)
+#define SEQ_LAUNCHED()                                                                                       \
+  do {                                                                                                       \
+    ++g_launches;                                                                                            \
+    cudaError_t _e = cudaGetLastError();                                                                     \
+    if (_e != cudaSuccess) return failf(KB2SEQ_ERR_CUDA, "launch at line %d: %s", __LINE__, cudaGetErrorString(_e)); \
+  } while (0)
+
+template <typename T> __device__ __forceinline__ float ldf(const T* p, long long i);
+template <> __device__ __forceinline__ float ldf<float>(const float* p, long long i) { return p[i]; }
+template <> __device__ __forceinline__ float ldf<bf16>(const bf16* p, long long i) { return __bfloat162float(p[i]); }
+template <typename T> __device__ __forceinline__ void stf(T* p, long long i, float v);
+template <> __device__ __forceinline__ void stf<float>(float* p, long long i, float v) { p[i] = v; }
+template <> __device__ __forceinline__ void stf<bf16>(bf16* p, long long i, float v) { p[i] = __float2bfloat16_rn(v); }
+
+__device__ __forceinline__ float ld_dt(const void* p, int dt, long long i) {
+  return dt ? __bfloat162float(((const bf16*)p)[i]) : ((const float*)p)[i];
+}
+__device__ __forceinline__ void st_dt(void* p, int dt, long long i, float v) {
+  if (dt) ((bf16*)p)[i] = __float2bfloat16_rn(v); else ((float*)p)[i] = v;
+}
+
+__device__ __forceinline__ float gelu_tanh(float z) {
+  return 0.5f * z * (1.f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z)));
+}
+__device__ __forceinline__ float silu(float z) { return z / (1.f + expf(-z)); }
+__device__ __forceinline__ float softplus(float z) { return z > 20.f ? z : log1pf(expf(z)); }
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+  for (int o = 16; o; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  return v;
+}
+// sum over the block; `red` holds 32 floats; every thread gets the result
+__device__ __forceinline__ float block_sum(float v, float* red) {
+  v = warp_sum(v);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = (blockDim.x + 31) >> 5;
+  __syncthreads();
+  if (lane == 0) red[warp] = v;
+  __syncthreads();
+  float t = 0.f;
+  for (int i = 0; i < nw; ++i) t += red[i];
+  return t;
+}
+
+// ------------------------------------------------------------------------------------------------ embedding
+template <typename T>
+__global__ void embed_scale_kernel(const T* __restrict__ table, const int* __restrict__ tokens, float* __restrict__ x, int W,
+                                   float scale) {
+  const long long t = blockIdx.x;
+  const long long row = tokens[t];
+  for (int d = threadIdx.x; d < W; d += blockDim.x) x[t * W + d] = ldf(table, row * W + d) * scale;
+}
+
+// ------------------------------------------------------------------------------------------------ GEMM
+// C[M,N] = A[M,K] * B[N,K]^T.  64x64 tile, 16-wide K steps, 4x4 outputs per thread, fp32 FMA.  Each output sums its K products
+// in the same order whatever M and N are, so a row's result does not depend on which other rows share the launch.
+template <typename TA, typename TB, typename TC>
+__global__ void __launch_bounds__(256) gemm_nt_kernel(const TA* __restrict__ A, long long lda, const TB* __restrict__ B, long long ldb,
+                                                      TC* __restrict__ C, long long ldc, int M, int N, int K, long long sA,
+                                                      long long sB, long long sC) {
+  constexpr int BM = 64, BN = 64, BK = 16;
+  __shared__ float As[BK][BM + 4], Bs[BK][BN + 4];
+  A += (long long)blockIdx.z * sA;
+  B += (long long)blockIdx.z * sB;
+  C += (long long)blockIdx.z * sC;
+  const int tid = threadIdx.x, tx = tid & 15, ty = tid >> 4;
+  const int m0 = blockIdx.y * BM, n0 = blockIdx.x * BN;
+  float acc[4][4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i)
+#pragma unroll
+    for (int j = 0; j < 4; ++j) acc[i][j] = 0.f;
+  for (int k0 = 0; k0 < K; k0 += BK) {
+#pragma unroll
+    for (int it = 0; it < 4; ++it) {
+      const int i = tid + it * 256, r = i >> 4, c = i & 15;
+      const int m = m0 + r, n = n0 + r, k = k0 + c;
+      As[c][r] = (m < M && k < K) ? ldf(A, (long long)m * lda + k) : 0.f;
+      Bs[c][r] = (n < N && k < K) ? ldf(B, (long long)n * ldb + k) : 0.f;
+    }
+    __syncthreads();
+#pragma unroll
+    for (int kk = 0; kk < BK; ++kk) {
+      float a[4], b[4];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) a[i] = As[kk][ty * 4 + i];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) b[j] = Bs[kk][tx * 4 + j];
+#pragma unroll
+      for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) acc[i][j] = fmaf(a[i], b[j], acc[i][j]);
+    }
+    __syncthreads();
+  }
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const int m = m0 + ty * 4 + i;
+    if (m >= M) continue;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int n = n0 + tx * 4 + j;
+      if (n < N) stf(C, (long long)m * ldc + n, acc[i][j]);
+    }
+  }
+}
+
+// Few rows (decode): one warp per output column, all M <= MR rows at once, so the weight matrix is read once at full width.
+template <typename TA, typename TB, typename TC, int MR>
+__global__ void __launch_bounds__(256) gemv_nt_kernel(const TA* __restrict__ A, long long lda, const TB* __restrict__ B, long long ldb,
+                                                      TC* __restrict__ C, long long ldc, int M, int N, int K, long long sA,
+                                                      long long sB, long long sC) {
+  A += (long long)blockIdx.z * sA;
+  B += (long long)blockIdx.z * sB;
+  C += (long long)blockIdx.z * sC;
+  const int lane = threadIdx.x & 31;
+  const int n = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (n >= N) return;
+  float acc[MR];
+#pragma unroll
+  for (int m = 0; m < MR; ++m) acc[m] = 0.f;
+  const TB* b = B + (long long)n * ldb;
+  for (int k = lane; k < K; k += 32) {
+    const float w = ldf(b, k);
+#pragma unroll
+    for (int m = 0; m < MR; ++m)
+      if (m < M) acc[m] = fmaf(ldf(A, (long long)m * lda + k), w, acc[m]);
+  }
+#pragma unroll
+  for (int m = 0; m < MR; ++m) {
+    const float v = warp_sum(acc[m]);
+    if (lane == 0 && m < M) stf(C, (long long)m * ldc + n, v);
+  }
+}
+
+template <typename TA, typename TB, typename TC>
+static void launch_gemm(const void* A, long long lda, const void* B, long long ldb, void* C, long long ldc, int M, int N, int K,
+                        int batch, long long sA, long long sB, long long sC, cudaStream_t s) {
+  if (M <= 8) {
+    dim3 grid((N + 7) / 8, 1, batch);
+    gemv_nt_kernel<TA, TB, TC, 8><<<grid, 256, 0, s>>>((const TA*)A, lda, (const TB*)B, ldb, (TC*)C, ldc, M, N, K, sA, sB, sC);
+  } else {
+    dim3 grid((N + 63) / 64, (M + 63) / 64, batch);
+    gemm_nt_kernel<TA, TB, TC><<<grid, 256, 0, s>>>((const TA*)A, lda, (const TB*)B, ldb, (TC*)C, ldc, M, N, K, sA, sB, sC);
+  }
+}
+
+// ------------------------------------------------------------------------------------------------ residual update + norm
+// One block per token row.  x (fp32) += norm_a(y) where norm_a is a layer norm (y_mode 1: weight wa, bias ba), an RMS norm
+// (y_mode 2: weight wa) or absent (y == nullptr); x += x0 if given; then h = layer_norm(x; wb, bb) if h is given.
+// Variances are means of squared deviations (two passes over the row held in shared memory).
+__global__ void __launch_bounds__(256) residual_norm_kernel(float* __restrict__ x, const float* __restrict__ y, int y_mode,
+                                                            const float* __restrict__ wa, const float* __restrict__ ba,
+                                                            const float* __restrict__ x0, const float* __restrict__ wb,
+                                                            const float* __restrict__ bb, void* __restrict__ h, int dt_h, int W,
+                                                            float eps) {
+  extern __shared__ float rowbuf[];
+  __shared__ float red[32];
+  const long long row = blockIdx.x;
+  float* xr = x + row * W;
+  const float inv_w = 1.f / (float)W;
+  if (y != nullptr) {
+    const float* yr = y + row * W;
+    float s = 0.f;
+    for (int d = threadIdx.x; d < W; d += blockDim.x) {
+      const float v = yr[d];
+      rowbuf[d] = v;
+      s += y_mode == 1 ? v : v * v;
+    }
+    s = block_sum(s, red);
+    float mean = 0.f, rstd;
+    if (y_mode == 1) {
+      mean = s * inv_w;
+      float q = 0.f;
+      for (int d = threadIdx.x; d < W; d += blockDim.x) {
+        const float c = rowbuf[d] - mean;
+        q += c * c;
+      }
+      q = block_sum(q, red);
+      rstd = 1.f / sqrtf(q * inv_w + eps);
+    } else {
+      rstd = 1.f / sqrtf(s * inv_w + eps);
+    }
+    for (int d = threadIdx.x; d < W; d += blockDim.x) {
+      float v = (rowbuf[d] - mean) * rstd * wa[d];
+      if (y_mode == 1) v += ba[d];
+      v += xr[d];
+      if (x0 != nullptr) v += x0[row * W + d];
+      xr[d] = v;
+      rowbuf[d] = v;
+    }
+  } else {
+    for (int d = threadIdx.x; d < W; d += blockDim.x) {
+      float v = xr[d];
+      if (x0 != nullptr) {
+        v += x0[row * W + d];
+        xr[d] = v;
+      }
+      rowbuf[d] = v;
+    }
+  }
+  if (h == nullptr) return;
+  float s = 0.f;
+  for (int d = threadIdx.x; d < W; d += blockDim.x) s += rowbuf[d];
+  const float mean = block_sum(s, red) * inv_w;
+  float q = 0.f;
+  for (int d = threadIdx.x; d < W; d += blockDim.x) {
+    const float c = rowbuf[d] - mean;
+    q += c * c;
+  }
+  q = block_sum(q, red);
+  const float rstd = 1.f / sqrtf(q * inv_w + eps);
+  for (int d = threadIdx.x; d < W; d += blockDim.x) st_dt(h, dt_h, row * W + d, (rowbuf[d] - mean) * rstd * wb[d] + bb[d]);
+}
+
+// ------------------------------------------------------------------------------------------------ elementwise
+__global__ void act_mul_kernel(const void* __restrict__ in, int dt_in, void* __restrict__ out, int dt_out, long long T, int F) {
+  const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= T * F) return;
+  const long long t = i / F;
+  const int f = (int)(i - t * F);
+  const float a = ld_dt(in, dt_in, t * 2 * F + f), b = ld_dt(in, dt_in, t * 2 * F + F + f);
+  st_dt(out, dt_out, i, gelu_tanh(a) * b);
+}
+
+__global__ void side_gate_kernel(const float* __restrict__ g, const void* __restrict__ table, int dt_table, long long table_ld,
+                                 const int* __restrict__ tokens, int col0, int dim, long long T, void* __restrict__ out, int dt_out) {
+  const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= T * dim) return;
+  const long long t = i / dim;
+  const int d = (int)(i - t * dim);
+  const float e = ld_dt(table, dt_table, (long long)tokens[t] * table_ld + col0 + d);
+  st_dt(out, dt_out, i, gelu_tanh(g[i]) * e);
+}
+
+// ------------------------------------------------------------------------------------------------ latent attention
+// Rotation angle pos * freq reduced in fp64, sin / cos in fp32.
+__device__ __forceinline__ void rot_cs(int pos, double freq, float amp, float* c, float* s) {
+  double a = (double)pos * freq;
+  a -= 6.283185307179586476925286766559 * rint(a * 0.15915494309189533576888376337251);
+  float sf, cf;
+  sincosf((float)a, &sf, &cf);
+  *c = cf * amp;
+  *s = sf * amp;
+}
+
+// proj [T, ldp] fp32 = [q (H x (dn + dr)) | latent (r) | shared rotated key (dr)].  Per token: RMS-normed latent and rotated key part
+// go to the page the token's position maps to; the query's rotated parts are rotated in place.
+__global__ void __launch_bounds__(128) latent_prep_kernel(float* __restrict__ proj, long long ldp, int H, int dn, int dr, int r,
+                                                          const float* __restrict__ cw, float eps, const double* __restrict__ freq,
+                                                          int rot_dims, float amp, const int* __restrict__ positions,
+                                                          const int* __restrict__ seq_of, const int* __restrict__ pages, int max_pages,
+                                                          int page_size, void* __restrict__ ckv, void* __restrict__ kr, int dt_cache) {
+  __shared__ float red[32];
+  const long long t = blockIdx.x;
+  const int pos = positions[t];
+  float* p = proj + t * ldp;
+  const long long slot = (long long)pages[(long long)seq_of[t] * max_pages + pos / page_size] * page_size + pos % page_size;
+  const float* lat = p + (long long)H * (dn + dr);
+  float ss = 0.f;
+  for (int d = threadIdx.x; d < r; d += blockDim.x) ss += lat[d] * lat[d];
+  ss = block_sum(ss, red);
+  const float rstd = 1.f / sqrtf(ss / (float)r + eps);
+  for (int d = threadIdx.x; d < r; d += blockDim.x) st_dt(ckv, dt_cache, slot * r + d, lat[d] * rstd * cw[d]);
+  const int half = rot_dims / 2;
+  // (H + 1) vectors of dr: the heads' query parts (in place) and the shared key part (to the cache)
+  for (int i = threadIdx.x; i < (H + 1) * half; i += blockDim.x) {
+    const int hh = i / half, j = i - hh * half;
+    float c, s;
+    rot_cs(pos, freq[j], amp, &c, &s);
+    if (hh < H) {
+      float* q = p + (long long)hh * (dn + dr) + dn;
+      const float u = q[2 * j], v = q[2 * j + 1];
+      q[2 * j] = u * c - v * s;
+      q[2 * j + 1] = v * c + u * s;
+    } else {
+      const float* k = lat + r;
+      const float u = k[2 * j], v = k[2 * j + 1];
+      st_dt(kr, dt_cache, slot * dr + 2 * j, u * c - v * s);
+      st_dt(kr, dt_cache, slot * dr + 2 * j + 1, v * c + u * s);
+    }
+  }
+  for (int d = rot_dims + threadIdx.x; d < dr; d += blockDim.x) st_dt(kr, dt_cache, slot * dr + d, lat[r + d]);
+}
+
+// Absorbed form: score(t, h, j) = (q_abs[t,h] . c_j + q_rot[t,h] . kr_j) * scale over the keys j of the token's sequence with
+// 0 <= pos - j < window; the softmax denominator also holds exp(sink_h) (a key with no value: running max starts at the sink,
+// running sum at 1).  Output: sum_j p_j c_j (the value up-projection follows as a per-head GEMM).
+// One block per (token, group of HG heads); keys in tiles of KT, shared by the heads of the group.
+constexpr int kAttnThreads = 256, kAttnAcc = 16;
+__global__ void __launch_bounds__(kAttnThreads) latent_window_attn_kernel(
+    const float* __restrict__ q_abs, const float* __restrict__ proj, long long ldp, int H, int HG, int dn, int dr, int r,
+    const void* __restrict__ ckv, const void* __restrict__ kr, int dt_cache, const int* __restrict__ positions,
+    const int* __restrict__ seq_of, const int* __restrict__ pages, int max_pages, int page_size, const float* __restrict__ sinks,
+    float scale, int window, int KT, float* __restrict__ out) {
+  extern __shared__ __align__(16) float sm[];
+  const int D = r + dr, DP = D + 1;
+  long long* krow = (long long*)sm;       // [KT] cache rows of the tile's keys
+  float* qs = sm + 2 * KT;                // [HG][D]
+  float* kt = qs + HG * D;                // [KT][DP]
+  float* pr = kt + KT * DP;               // [HG][KT]
+  float* m_run = pr + HG * KT;            // [HG]
+  float* l_run = m_run + HG;              // [HG]
+  float* alpha = l_run + HG;              // [HG]
+  const long long t = blockIdx.x;
+  const int h0 = blockIdx.y * HG;
+  const int nh = min(HG, H - h0);
+  const int pos = positions[t], seq = seq_of[t];
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  for (int i = tid; i < nh * D; i += kAttnThreads) {
+    const int hh = i / D, d = i - hh * D;
+    qs[i] = d < r ? q_abs[(t * H + h0 + hh) * r + d] : proj[t * ldp + (long long)(h0 + hh) * (dn + dr) + dn + (d - r)];
+  }
+  if (tid < nh) {
+    m_run[tid] = sinks[h0 + tid];
+    l_run[tid] = 1.f;
+  }
+  float acc[kAttnAcc];
+#pragma unroll
+  for (int a = 0; a < kAttnAcc; ++a) acc[a] = 0.f;
+  const int j_lo = max(0, pos - window + 1);
+  for (int j0 = j_lo; j0 <= pos; j0 += KT) {
+    const int nk = min(KT, pos - j0 + 1);
+    __syncthreads();
+    if (tid < nk) {
+      const int j = j0 + tid;
+      krow[tid] = (long long)pages[(long long)seq * max_pages + j / page_size] * page_size + j % page_size;
+    }
+    __syncthreads();
+    for (int i = tid; i < nk * D; i += kAttnThreads) {
+      const int k = i / D, d = i - k * D;
+      kt[k * DP + d] = d < r ? ld_dt(ckv, dt_cache, krow[k] * r + d) : ld_dt(kr, dt_cache, krow[k] * dr + (d - r));
+    }
+    __syncthreads();
+    // scores and the running softmax: a warp per head, a lane per key
+    for (int hh = warp; hh < nh; hh += kAttnThreads / 32) {
+      const float* qh = qs + hh * D;
+      const float m_old = m_run[hh];
+      float m_new = m_old;
+      for (int kb = 0; kb < nk; kb += 32) {
+        const int k = kb + lane;
+        float sc = -INFINITY;
+        if (k < nk) {
+          const float* kk = kt + k * DP;
+          float dot = 0.f;
+          for (int d = 0; d < D; ++d) dot = fmaf(qh[d], kk[d], dot);
+          sc = dot * scale;
+        }
+        if (k < KT) pr[hh * KT + k] = sc;
+        m_new = fmaxf(m_new, warp_max(sc));
+      }
+      float lsum = 0.f;
+      for (int kb = 0; kb < nk; kb += 32) {
+        const int k = kb + lane;
+        float p = 0.f;
+        if (k < nk) {
+          p = expf(pr[hh * KT + k] - m_new);
+          pr[hh * KT + k] = p;
+        }
+        lsum += warp_sum(p);
+      }
+      if (lane == 0) {
+        const float al = expf(m_old - m_new);
+        alpha[hh] = al;
+        l_run[hh] = l_run[hh] * al + lsum;
+        m_run[hh] = m_new;
+      }
+    }
+    __syncthreads();
+#pragma unroll
+    for (int a = 0; a < kAttnAcc; ++a) {
+      const int i = tid + a * kAttnThreads;
+      if (i < nh * r) {
+        const int hh = i / r, d = i - hh * r;
+        float v = acc[a] * alpha[hh];
+        const float* ph = pr + hh * KT;
+        for (int k = 0; k < nk; ++k) v = fmaf(ph[k], kt[k * DP + d], v);
+        acc[a] = v;
+      }
+    }
+  }
+  __syncthreads();
+#pragma unroll
+  for (int a = 0; a < kAttnAcc; ++a) {
+    const int i = tid + a * kAttnThreads;
+    if (i < nh * r) {
+      const int hh = i / r, d = i - hh * r;
+      out[(t * H + h0 + hh) * r + d] = acc[a] / l_run[hh];
+    }
+  }
+}
+
+// ------------------------------------------------------------------------------------------------ short convolution + delta rule
+// y[t, c] = silu(sum_j taps[c, j] * x[i - (K - 1) + j, c]) with i the token's index in its portion; inputs before the portion come
+// from the sequence's carried tail (the last K - 1 inputs of earlier portions, zeros at the start of a sequence).
+__global__ void conv_silu_kernel(const float* __restrict__ proj, long long ldp, int C, int K, const float* __restrict__ taps,
+                                 const float* __restrict__ tail, const int* __restrict__ seq_of, const int* __restrict__ cu,
+                                 const int* __restrict__ slots, long long T, float* __restrict__ out) {
+  const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= T * C) return;
+  const long long t = idx / C;
+  const int c = (int)(idx - t * C);
+  const int s = seq_of[t];
+  const int i = (int)(t - cu[s]);
+  const float* tl = tail + ((long long)slots[s] * C + c) * (K - 1);
+  float acc = 0.f;
+  for (int j = 0; j < K; ++j) {
+    const int src = i - (K - 1) + j;
+    const float xv = src >= 0 ? proj[(t - i + src) * ldp + c] : tl[(K - 1) + src];
+    acc = fmaf(taps[(long long)c * K + j], xv, acc);
+  }
+  out[idx] = silu(acc);
+}
+
+// after the convolution: the tail becomes the last K - 1 inputs seen so far (one thread per (sequence, channel), ascending order)
+__global__ void conv_tail_kernel(const float* __restrict__ proj, long long ldp, int C, int K, float* __restrict__ tail,
+                                 const int* __restrict__ cu, const int* __restrict__ slots, int S) {
+  const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= (long long)S * C) return;
+  const int s = (int)(idx / C), c = (int)(idx - (long long)s * C);
+  const int t0 = cu[s], n = cu[s + 1] - cu[s];
+  float* tl = tail + ((long long)slots[s] * C + c) * (K - 1);
+  for (int j = 0; j < K - 1; ++j) {
+    const int src = n - (K - 1) + j;         // index in the portion of the input that lands in tail[j]
+    tl[j] = src >= 0 ? proj[(long long)(t0 + src) * ldp + c] : tl[j + n];
+  }
+}
+
+// One block per (sequence, head); thread j owns column j of the head's state S [dk][dv] (kept in shared memory for the portion).
+// conv [T, C] = silu(conv(q | k | v)); proj holds the gate (g_off), the decay input (a_off) and the write-strength input (b_off).
+constexpr int kDeltaTile = 16;
+__global__ void __launch_bounds__(1024) delta_rule_kernel(const float* __restrict__ conv, int C, const float* __restrict__ proj,
+                                                          long long ldp, int g_off, int a_off, int b_off, int H, int Hk, int dk, int dv,
+                                                          const float* __restrict__ A_log, const float* __restrict__ dt_bias,
+                                                          const float* __restrict__ norm_w, float eps, float* __restrict__ state,
+                                                          const int* __restrict__ cu, const int* __restrict__ slots,
+                                                          void* __restrict__ out, int dt_out) {
+  extern __shared__ float sm[];
+  float* S = sm;                                  // [dk][dv]
+  float* qn = S + (long long)dk * dv;             // [tile][dk]
+  float* kn = qn + kDeltaTile * dk;               // [tile][dk]
+  float* ob = kn + kDeltaTile * dk;               // [tile][dv]
+  float* beta = ob + kDeltaTile * dv;             // [tile]
+  float* dec = beta + kDeltaTile;                 // [tile]
+  const int s = blockIdx.x, h = blockIdx.y, hk = h / (H / Hk);
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, nw = blockDim.x >> 5;
+  const int t0 = cu[s], n = cu[s + 1] - cu[s];
+  float* Sg = state + ((long long)slots[s] * H + h) * dk * dv;
+  for (int i = tid; i < dk * dv; i += blockDim.x) S[i] = Sg[i];
+  const float a_neg = -expf(A_log[h]), bias = dt_bias[h], qscale = rsqrtf((float)dk);
+  const int q_col = hk * dk, k_col = Hk * dk + hk * dk, v_col = 2 * Hk * dk + h * dv;
+  for (int b0 = 0; b0 < n; b0 += kDeltaTile) {
+    const int nt = min(kDeltaTile, n - b0);
+    __syncthreads();
+    for (int tt = warp; tt < nt; tt += nw) {
+      const float* row = conv + (long long)(t0 + b0 + tt) * C;
+      float sq = 0.f, sk = 0.f;
+      for (int i = lane; i < dk; i += 32) {
+        const float qv = row[q_col + i], kv = row[k_col + i];
+        sq += qv * qv;
+        sk += kv * kv;
+      }
+      sq = warp_sum(sq);
+      sk = warp_sum(sk);
+      const float rq = qscale / sqrtf(sq + 1e-6f), rk = 1.f / sqrtf(sk + 1e-6f);
+      for (int i = lane; i < dk; i += 32) {
+        qn[tt * dk + i] = row[q_col + i] * rq;
+        kn[tt * dk + i] = row[k_col + i] * rk;
+      }
+      if (lane == 0) {
+        const float* pr = proj + (long long)(t0 + b0 + tt) * ldp;
+        beta[tt] = 1.f / (1.f + expf(-pr[b_off + h]));
+        dec[tt] = expf(a_neg * softplus(pr[a_off + h] + bias));
+      }
+    }
+    __syncthreads();
+    if (tid < dv) {
+      for (int tt = 0; tt < nt; ++tt) {
+        const float g = dec[tt];
+        const float* kk = kn + tt * dk;
+        const float* qq = qn + tt * dk;
+        float sk = 0.f;
+        for (int i = 0; i < dk; ++i) {
+          const float sv = S[i * dv + tid] * g;
+          S[i * dv + tid] = sv;
+          sk = fmaf(sv, kk[i], sk);
+        }
+        const float u = beta[tt] * (conv[(long long)(t0 + b0 + tt) * C + v_col + tid] - sk);
+        float o = 0.f;
+        for (int i = 0; i < dk; ++i) {
+          const float sv = fmaf(kk[i], u, S[i * dv + tid]);
+          S[i * dv + tid] = sv;
+          o = fmaf(sv, qq[i], o);
+        }
+        ob[tt * dv + tid] = o;
+      }
+    }
+    __syncthreads();
+    for (int tt = warp; tt < nt; tt += nw) {
+      float ss = 0.f;
+      for (int j = lane; j < dv; j += 32) ss += ob[tt * dv + j] * ob[tt * dv + j];
+      ss = warp_sum(ss);
+      const float rstd = 1.f / sqrtf(ss / (float)dv + eps);
+      const long long t = t0 + b0 + tt;
+      for (int j = lane; j < dv; j += 32)
+        st_dt(out, dt_out, (t * H + h) * dv + j, ob[tt * dv + j] * rstd * norm_w[j] * silu(proj[t * ldp + g_off + h * dv + j]));
+    }
+  }
+  __syncthreads();
+  for (int i = tid; i < dk * dv; i += blockDim.x) Sg[i] = S[i];
+}
+
+}  // namespace kb2seq
+
+using namespace kb2seq;
+
+static bool bad_dt(int dt) { return dt != 0 && dt != 1; }
+
+extern "C" {
+
+KB2SEQ_API const char* kb2_seq_last_error(void) { return g_err; }
+KB2SEQ_API long long kb2_seq_total_launches(void) { return g_launches; }
+
+KB2SEQ_API int kb2_seq_embed(const void* table, int dt, const int* tokens, float* x, int T, int W, float scale, void* stream) {
+  if (!table || !tokens || !x || T <= 0 || W <= 0 || bad_dt(dt)) return failf(KB2SEQ_ERR_VALUE, "embed: bad argument");
+  if (dt) embed_scale_kernel<bf16><<<T, 128, 0, (cudaStream_t)stream>>>((const bf16*)table, tokens, x, W, scale);
+  else embed_scale_kernel<float><<<T, 128, 0, (cudaStream_t)stream>>>((const float*)table, tokens, x, W, scale);
+  SEQ_LAUNCHED();
+  return KB2SEQ_OK;
+}
+
+KB2SEQ_API int kb2_seq_gemm(const void* A, int dtA, long long lda, const void* B, int dtB, long long ldb, void* C, int dtC,
+                            long long ldc, int M, int N, int K, int batch, long long sA, long long sB, long long sC, void* stream) {
+  if (!A || !B || !C || M <= 0 || N <= 0 || K <= 0 || batch <= 0 || batch > 65535 || bad_dt(dtA) || bad_dt(dtB) || bad_dt(dtC))
+    return failf(KB2SEQ_ERR_VALUE, "gemm: bad argument (M=%d N=%d K=%d batch=%d)", M, N, K, batch);
+  cudaStream_t s = (cudaStream_t)stream;
+  const int code = dtA * 4 + dtB * 2 + dtC;
+#define G(TA, TB, TC) launch_gemm<TA, TB, TC>(A, lda, B, ldb, C, ldc, M, N, K, batch, sA, sB, sC, s)
+  switch (code) {
+    case 0: G(float, float, float); break;
+    case 1: G(float, float, bf16); break;
+    case 2: G(float, bf16, float); break;
+    case 3: G(float, bf16, bf16); break;
+    case 4: G(bf16, float, float); break;
+    case 5: G(bf16, float, bf16); break;
+    case 6: G(bf16, bf16, float); break;
+    default: G(bf16, bf16, bf16); break;
+  }
+#undef G
+  SEQ_LAUNCHED();
+  return KB2SEQ_OK;
+}
+
+KB2SEQ_API int kb2_seq_residual_norm(float* x, const float* y, int y_mode, const float* wa, const float* ba, const float* x0,
+                                     const float* wb, const float* bb, void* h, int dt_h, int T, int W, float eps, void* stream) {
+  if (!x || T <= 0 || W <= 0 || bad_dt(dt_h)) return failf(KB2SEQ_ERR_VALUE, "residual_norm: bad argument");
+  if (y && (y_mode < 1 || y_mode > 2 || !wa || (y_mode == 1 && !ba))) return failf(KB2SEQ_ERR_VALUE, "residual_norm: norm of y needs its weights");
+  if (h && (!wb || !bb)) return failf(KB2SEQ_ERR_VALUE, "residual_norm: output norm needs weight and bias");
+  const size_t smem = (size_t)W * 4;
+  if (smem > 200 * 1024) return failf(KB2SEQ_ERR_VALUE, "residual_norm: width %d too large", W);
+  if (smem > 48 * 1024) SEQ_CUDA(cudaFuncSetAttribute(residual_norm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+  residual_norm_kernel<<<T, 256, smem, (cudaStream_t)stream>>>(x, y, y_mode, wa, ba, x0, wb, bb, h, dt_h, W, eps);
+  SEQ_LAUNCHED();
+  return KB2SEQ_OK;
+}
+
+KB2SEQ_API int kb2_seq_act_mul(const void* in, int dt_in, void* out, int dt_out, int T, int F, void* stream) {
+  if (!in || !out || T <= 0 || F <= 0 || bad_dt(dt_in) || bad_dt(dt_out)) return failf(KB2SEQ_ERR_VALUE, "act_mul: bad argument");
+  const long long n = (long long)T * F;
+  act_mul_kernel<<<(unsigned)((n + 255) / 256), 256, 0, (cudaStream_t)stream>>>(in, dt_in, out, dt_out, T, F);
+  SEQ_LAUNCHED();
+  return KB2SEQ_OK;
+}
+
+KB2SEQ_API int kb2_seq_side_gate(const float* g, const void* table, int dt_table, long long table_ld, const int* tokens, int col0,
+                                 int dim, int T, void* out, int dt_out, void* stream) {
+  if (!g || !table || !tokens || !out || T <= 0 || dim <= 0 || col0 < 0 || bad_dt(dt_table) || bad_dt(dt_out))
+    return failf(KB2SEQ_ERR_VALUE, "side_gate: bad argument");
+  const long long n = (long long)T * dim;
+  side_gate_kernel<<<(unsigned)((n + 255) / 256), 256, 0, (cudaStream_t)stream>>>(g, table, dt_table, table_ld, tokens, col0, dim, T, out,
+                                                                                  dt_out);
+  SEQ_LAUNCHED();
+  return KB2SEQ_OK;
+}
+
+KB2SEQ_API int kb2_seq_latent_prep(float* proj, long long ldp, int T, int H, int dn, int dr, int r, const float* cw, float eps,
+                                   const double* freq, int rot_dims, float amp, const int* positions, const int* seq_of,
+                                   const int* pages, int max_pages, int page_size, void* ckv, void* kr, int dt_cache, void* stream) {
+  if (!proj || !cw || !freq || !positions || !seq_of || !pages || !ckv || !kr || T <= 0 || H <= 0 || dn < 0 || dr < 0 || r <= 0 ||
+      rot_dims < 0 || rot_dims > dr || (rot_dims & 1) || page_size <= 0 || max_pages <= 0 || bad_dt(dt_cache))
+    return failf(KB2SEQ_ERR_VALUE, "latent_prep: bad argument");
+  latent_prep_kernel<<<T, 128, 0, (cudaStream_t)stream>>>(proj, ldp, H, dn, dr, r, cw, eps, freq, rot_dims, amp, positions, seq_of, pages,
+                                                          max_pages, page_size, ckv, kr, dt_cache);
+  SEQ_LAUNCHED();
+  return KB2SEQ_OK;
+}
+
+KB2SEQ_API int kb2_seq_latent_window_attn(const float* q_abs, const float* proj, long long ldp, int T, int H, int dn, int dr, int r,
+                                          const void* ckv, const void* kr, int dt_cache, const int* positions, const int* seq_of,
+                                          const int* pages, int max_pages, int page_size, const float* sinks, float scale, int window,
+                                          float* out, void* stream) {
+  if (!q_abs || !proj || !ckv || !kr || !positions || !seq_of || !pages || !sinks || !out || T <= 0 || H <= 0 || r <= 0 || dr < 0 ||
+      window <= 0 || bad_dt(dt_cache))
+    return failf(KB2SEQ_ERR_VALUE, "latent_window_attn: bad argument");
+  if (r > kAttnThreads * kAttnAcc) return failf(KB2SEQ_ERR_VALUE, "latent_window_attn: latent size %d > %d", r, kAttnThreads * kAttnAcc);
+  int HG = kAttnThreads * kAttnAcc / r;
+  if (HG > H) HG = H;
+  if (HG > 8) HG = 8;
+  const int D = r + dr;
+  int KT = 32;
+  auto smem_of = [&](int hg, int kt) { return (size_t)(hg * D + kt * (D + 1) + hg * kt + 3 * hg) * 4 + (size_t)kt * 8; };
+  while (HG > 1 && smem_of(HG, KT) > 200 * 1024) --HG;
+  const size_t smem = smem_of(HG, KT);
+  if (smem > 200 * 1024) return failf(KB2SEQ_ERR_VALUE, "latent_window_attn: latent + rotated size %d too large", D);
+  if (smem > 48 * 1024) SEQ_CUDA(cudaFuncSetAttribute(latent_window_attn_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+  dim3 grid(T, (H + HG - 1) / HG);
+  latent_window_attn_kernel<<<grid, kAttnThreads, smem, (cudaStream_t)stream>>>(q_abs, proj, ldp, H, HG, dn, dr, r, ckv, kr, dt_cache, positions,
+                                                                                 seq_of, pages, max_pages, page_size, sinks, scale, window, KT,
+                                                                                 out);
+  SEQ_LAUNCHED();
+  return KB2SEQ_OK;
+}
+
+KB2SEQ_API int kb2_seq_conv_silu(const float* proj, long long ldp, int T, int S, int C, int K, const float* taps, float* tail,
+                                 const int* seq_of, const int* cu, const int* slots, float* out, void* stream) {
+  if (!proj || !taps || !tail || !seq_of || !cu || !slots || !out || T <= 0 || S <= 0 || C <= 0 || K <= 0)
+    return failf(KB2SEQ_ERR_VALUE, "conv_silu: bad argument");
+  const long long n = (long long)T * C;
+  conv_silu_kernel<<<(unsigned)((n + 255) / 256), 256, 0, (cudaStream_t)stream>>>(proj, ldp, C, K, taps, tail, seq_of, cu, slots, T, out);
+  SEQ_LAUNCHED();
+  if (K > 1) {
+    const long long m = (long long)S * C;
+    conv_tail_kernel<<<(unsigned)((m + 255) / 256), 256, 0, (cudaStream_t)stream>>>(proj, ldp, C, K, tail, cu, slots, S);
+    SEQ_LAUNCHED();
+  }
+  return KB2SEQ_OK;
+}
+
+KB2SEQ_API int kb2_seq_delta_rule(const float* conv, int C, const float* proj, long long ldp, int g_off, int a_off, int b_off, int S,
+                                  int H, int Hk, int dk, int dv, const float* A_log, const float* dt_bias, const float* norm_w, float eps,
+                                  float* state, const int* cu, const int* slots, void* out, int dt_out, void* stream) {
+  if (!conv || !proj || !A_log || !dt_bias || !norm_w || !state || !cu || !slots || !out || S <= 0 || H <= 0 || Hk <= 0 || H % Hk ||
+      dk <= 0 || dv <= 0 || bad_dt(dt_out))
+    return failf(KB2SEQ_ERR_VALUE, "delta_rule: bad argument");
+  if (dv > 1024) return failf(KB2SEQ_ERR_VALUE, "delta_rule: value size %d > 1024", dv);
+  const size_t smem = ((size_t)dk * dv + (size_t)kDeltaTile * (2 * dk + dv + 2)) * 4;
+  if (smem > 220 * 1024) return failf(KB2SEQ_ERR_VALUE, "delta_rule: a %d x %d state does not fit one block's shared memory", dk, dv);
+  if (smem > 48 * 1024) SEQ_CUDA(cudaFuncSetAttribute(delta_rule_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+  int threads = (dv + 31) / 32 * 32;
+  if (threads < 128) threads = 128;
+  dim3 grid(S, H);
+  delta_rule_kernel<<<grid, threads, smem, (cudaStream_t)stream>>>(conv, C, proj, ldp, g_off, a_off, b_off, H, Hk, dk, dv, A_log, dt_bias, norm_w,
+                                                                  eps, state, cu, slots, out, dt_out);
+  SEQ_LAUNCHED();
+  return KB2SEQ_OK;
+}
+
+}  // extern "C"

@@ -1,0 +1,182 @@
+"""ctypes binding of include/krasis_b200_seq.h (libkrasis_b200_seq.so) and thin tensor-level wrappers.
+
+The operators work on one step of a serving engine: a flat token axis with per-token and per-sequence int32 tables on the
+device (`StepTables`).  All arithmetic runs in the CUDA library; torch owns the buffers.  No fallback: a missing library is an
+ImportError that names the build command.
+"""
+import ctypes as C
+import os
+
+import torch
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(HERE, "_lib", "libkrasis_b200_seq.so")
+
+_P, _I, _L, _F = C.c_void_p, C.c_int, C.c_longlong, C.c_float
+SIGNATURES = {
+    "kb2_seq_last_error": (C.c_char_p, []),
+    "kb2_seq_total_launches": (C.c_longlong, []),
+    "kb2_seq_embed": (_I, [_P, _I, _P, _P, _I, _I, _F, _P]),
+    "kb2_seq_gemm": (_I, [_P, _I, _L, _P, _I, _L, _P, _I, _L, _I, _I, _I, _I, _L, _L, _L, _P]),
+    "kb2_seq_residual_norm": (_I, [_P, _P, _I, _P, _P, _P, _P, _P, _P, _I, _I, _I, _F, _P]),
+    "kb2_seq_act_mul": (_I, [_P, _I, _P, _I, _I, _I, _P]),
+    "kb2_seq_side_gate": (_I, [_P, _P, _I, _L, _P, _I, _I, _I, _P, _I, _P]),
+    "kb2_seq_latent_prep": (_I, [_P, _L, _I, _I, _I, _I, _I, _P, _F, _P, _I, _F, _P, _P, _P, _I, _I, _P, _P, _I, _P]),
+    "kb2_seq_latent_window_attn": (_I, [_P, _P, _L, _I, _I, _I, _I, _I, _P, _P, _I, _P, _P, _P, _I, _I, _P, _F, _I, _P, _P]),
+    "kb2_seq_conv_silu": (_I, [_P, _L, _I, _I, _I, _I, _P, _P, _P, _P, _P, _P, _P]),
+    "kb2_seq_delta_rule": (_I, [_P, _I, _P, _L, _I, _I, _I, _I, _I, _I, _I, _I, _P, _P, _P, _F, _P, _P, _P, _P, _I, _P]),
+}
+
+_lib = None
+
+
+def load():
+    global _lib
+    if _lib is None:
+        if not os.path.exists(LIB_PATH):
+            raise ImportError(f"{LIB_PATH} is missing: build it with `python -m krasis_b200.build --seq-only` "
+                              "(krasis_b200 has no CPU or PyTorch fallback)")
+        lib = C.CDLL(LIB_PATH)
+        for name, (res, args) in SIGNATURES.items():
+            fn = getattr(lib, name)
+            fn.restype, fn.argtypes = res, args
+        _lib = lib
+    return _lib
+
+
+class SeqOpsError(RuntimeError):
+    pass
+
+
+def check(rc: int):
+    if rc == 0:
+        return
+    msg = load().kb2_seq_last_error().decode()
+    if rc == 2:
+        raise ValueError(msg)
+    raise SeqOpsError(msg)
+
+
+def total_launches() -> int:
+    return int(load().kb2_seq_total_launches())
+
+
+def dt_code(dtype) -> int:
+    if dtype == torch.float32:
+        return 0
+    if dtype == torch.bfloat16:
+        return 1
+    raise ValueError(f"unsupported dtype {dtype}: float32 or bfloat16")
+
+
+def _s(t) -> int:
+    return torch.cuda.current_stream(t.device).cuda_stream
+
+
+def _cuda(t, name):
+    if not t.is_cuda:
+        raise ValueError(f"{name}: expected a CUDA tensor (krasis_b200 has no CPU path)")
+
+
+def _ptr(t):
+    return t.data_ptr() if t is not None else None
+
+
+class StepTables:
+    """The int32 tables of one step, packed into one pinned host buffer and copied to the device in one transfer.
+
+    entries: [(tokens, start_position, state_slot, page_list)] in batch order."""
+
+    def __init__(self, entries, device):
+        import numpy as np
+        S = len(entries)
+        T = sum(len(e[0]) for e in entries)
+        maxp = max(1, max(len(e[3]) for e in entries))
+        n = 3 * T + (S + 1) + S + S * maxp
+        host = torch.empty(n, dtype=torch.int32, pin_memory=torch.cuda.is_available())
+        a = host.numpy()
+        cu = 0
+        o_pos, o_seq, o_cu, o_slot, o_pg = T, 2 * T, 3 * T, 3 * T + S + 1, 3 * T + 2 * S + 1
+        a[o_pg:] = 0
+        for s, (toks, start, slot, pages) in enumerate(entries):
+            k = len(toks)
+            a[cu:cu + k] = np.asarray(toks, dtype=np.int32)
+            a[o_pos + cu:o_pos + cu + k] = np.arange(start, start + k, dtype=np.int32)
+            a[o_seq + cu:o_seq + cu + k] = s
+            a[o_cu + s] = cu
+            a[o_slot + s] = slot
+            a[o_pg + s * maxp:o_pg + s * maxp + len(pages)] = np.asarray(pages, dtype=np.int32)
+            cu += k
+        a[o_cu + S] = cu
+        self.T, self.S, self.max_pages = T, S, maxp
+        self.max_portion = max(len(e[0]) for e in entries)
+        self.buf = host.to(device, non_blocking=True)
+        self._host = host
+        self.tokens, self.positions, self.seq_of = self.buf[:T], self.buf[o_pos:o_pos + T], self.buf[o_seq:o_seq + T]
+        self.cu, self.slots, self.pages = self.buf[o_cu:o_cu + S + 1], self.buf[o_slot:o_slot + S], self.buf[o_pg:]
+        self.h2d_bytes = n * 4
+
+
+def embed(table: torch.Tensor, tokens: torch.Tensor, scale: float) -> torch.Tensor:
+    _cuda(table, "table")
+    T, W = tokens.shape[0], table.shape[1]
+    x = torch.empty((T, W), dtype=torch.float32, device=table.device)
+    check(load().kb2_seq_embed(table.data_ptr(), dt_code(table.dtype), tokens.data_ptr(), x.data_ptr(), T, W, float(scale), _s(table)))
+    return x
+
+
+def gemm(a: torch.Tensor, w: torch.Tensor, out_dtype=torch.float32, out: torch.Tensor = None) -> torch.Tensor:
+    """a [M, K] (row stride free) times w [N, K]^T -> [M, N]."""
+    _cuda(a, "a")
+    M, K = a.shape
+    N = w.shape[0]
+    if w.shape[1] != K or a.stride(1) != 1 or w.stride(1) != 1:
+        raise ValueError(f"gemm: shapes {tuple(a.shape)} x {tuple(w.shape)}")
+    if out is None:
+        out = torch.empty((M, N), dtype=out_dtype, device=a.device)
+    check(load().kb2_seq_gemm(a.data_ptr(), dt_code(a.dtype), a.stride(0), w.data_ptr(), dt_code(w.dtype), w.stride(0), out.data_ptr(),
+                              dt_code(out.dtype), out.stride(0), M, N, K, 1, 0, 0, 0, _s(a)))
+    return out
+
+
+def gemm_heads(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
+    """Per-head product: a [M, H, K] (any strides with unit last stride), w [H, N, K] -> out [M, H, N]."""
+    M, H, K = a.shape
+    N = w.shape[1]
+    if w.shape[0] != H or w.shape[2] != K or out.shape != (M, H, N) or a.stride(2) != 1 or out.stride(2) != 1 or not w.is_contiguous():
+        raise ValueError("gemm_heads: shape mismatch")
+    check(load().kb2_seq_gemm(a.data_ptr(), dt_code(a.dtype), a.stride(0), w.data_ptr(), dt_code(w.dtype), K, out.data_ptr(),
+                              dt_code(out.dtype), out.stride(0), M, N, K, H, a.stride(1), N * K, out.stride(1), _s(a)))
+    return out
+
+
+def residual_norm(x, y=None, y_norm=None, x0=None, out_norm=None, out_dtype=torch.float32, eps=1e-5):
+    """x (fp32, in place) += norm(y) [+ x0]; returns layer_norm(x) with out_norm = (weight, bias) or None.
+    y_norm = ("layer", w, b) | ("rms", w)."""
+    T, W = x.shape
+    mode, wa, ba = 0, None, None
+    if y is not None:
+        mode = 1 if y_norm[0] == "layer" else 2
+        wa, ba = y_norm[1], (y_norm[2] if mode == 1 else None)
+        if y.dtype != torch.float32 or not y.is_contiguous():
+            raise ValueError("residual_norm: y must be contiguous fp32")
+    h = torch.empty((T, W), dtype=out_dtype, device=x.device) if out_norm is not None else None
+    wb, bb = out_norm if out_norm is not None else (None, None)
+    check(load().kb2_seq_residual_norm(x.data_ptr(), _ptr(y), mode, _ptr(wa), _ptr(ba), _ptr(x0), _ptr(wb), _ptr(bb), _ptr(h),
+                                       dt_code(out_dtype), T, W, float(eps), _s(x)))
+    return h
+
+
+def act_mul(gate_up: torch.Tensor, out_dtype) -> torch.Tensor:
+    T, F2 = gate_up.shape
+    out = torch.empty((T, F2 // 2), dtype=out_dtype, device=gate_up.device)
+    check(load().kb2_seq_act_mul(gate_up.data_ptr(), dt_code(gate_up.dtype), out.data_ptr(), dt_code(out_dtype), T, F2 // 2, _s(gate_up)))
+    return out
+
+
+def side_gate(g: torch.Tensor, table: torch.Tensor, tokens: torch.Tensor, col0: int, out_dtype) -> torch.Tensor:
+    T, dim = g.shape
+    out = torch.empty((T, dim), dtype=out_dtype, device=g.device)
+    check(load().kb2_seq_side_gate(g.data_ptr(), table.data_ptr(), dt_code(table.dtype), table.stride(0), tokens.data_ptr(), col0, dim, T,
+                                   out.data_ptr(), dt_code(out_dtype), _s(g)))
+    return out
