@@ -1,0 +1,137 @@
+"""Throughput of a ragged-batch model (Vofelix) at layer sizes of real models, beside the framework's closest existing blocks at
+equal size: prefill tokens/s (one prompt, whole and in portions), decode tokens/s (several live requests, one token each per step),
+and per-mixer times — the gated delta mixer against the Gated-DeltaNet block, windowed latent attention against the MLA block.
+Random weights; device timing with CUDA events after warm-up; the weights of a step exceed the L2 cache."""
+import json
+
+import torch
+
+
+def _layer(kind, mixer, ff=None):
+    return {"type": kind, "mixer": mixer, "mlp": {"kind": "dense", "ff": ff} if ff else None}
+
+
+def bench_config(width=2048, window=1024, vocab=32768):
+    """Qwen3-Next's linear-attention geometry for the delta mixer, DeepSeek-V2-Lite's MLA geometry for latent attention."""
+    delta = {"heads": 32, "kv_heads": 16, "dim": 128, "vdim": 128, "conv": 4}
+    latent = {"heads": 16, "dim": 128, "rot_dim": 64, "vdim": 128, "kv_rank": 512, "scale": 192 ** -0.5, "mask": {"size": window},
+              "rot": {"base": 10000.0, "dims": 64, "scaling": {"factor": 40.0, "original": 4096, "fast": 32.0, "slow": 1.0}}}
+    layers = [_layer("delta", delta), _layer("delta", delta, ff=4 * width), _layer("latent_attention", latent, ff=4 * width),
+              _layer("delta", delta)]
+    return {"architecture": "Vofelix", "vocab": vocab, "width": width, "embedding": {"scale": 8.0}, "norm": {"eps": 1e-5},
+            "token_side": {"dim": 256}, "loop": {"start": 1, "stop": 3, "times": 2}, "layers": layers}, delta, latent
+
+
+def _time(fn, warmup, steps):
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(steps):
+        fn()
+    e1.record()
+    torch.cuda.synchronize()
+    return e0.elapsed_time(e1) / steps
+
+
+def run(args, peaks):
+    from . import seqops as ops
+    from .build import build_seq
+    build_seq()
+    from .scheduler import Scheduler
+    from .vofelix import VofelixConfig, VofelixModel
+    dev = torch.device("cuda", 0)
+    tokens = args.tokens or 4096
+    raw, delta, latent = bench_config()
+    cfg = VofelixConfig.from_dict(raw)
+    model = VofelixModel.random(cfg, seed=0, dtype=torch.bfloat16, device=0)
+    g = torch.Generator().manual_seed(0)
+    prompt = torch.randint(0, cfg.vocab, (tokens,), generator=g).tolist()
+    out = {"metric": "vofelix_prefill_tokens_per_s", "unit": "tokens/s", "n_gpus": 1, "steps": args.steps, "warmup": args.warmup,
+           "higher_is_better": True, "dtype": "bf16", "data": "synthetic (random weights and token ids)", "vs_baseline": None,
+           "config": {"model": "vofelix width 2048: 4 layers (3 delta 32/16 heads x 128, 1 latent 16 heads 128+64 / rank 512, window 1024), "
+                               "span 1..3 run twice = 6 layer runs, ff 8192, side 256", "prompt_tokens": tokens,
+                      "l2": "weights of one step (about 0.4 GB) exceed L2"}}
+
+    # ---- prefill: the whole prompt in one step, then in portions of 512
+    launches0 = ops.total_launches()
+
+    def prefill(portion):
+        s = Scheduler(model, max_tokens=tokens + 64, max_requests=4)
+        at = 0
+        while at < tokens:
+            n = min(portion, tokens - at)
+            lg = s.step([("p", prompt[at:at + n], [n - 1] if at + n == tokens else [])])
+            at += n
+        s.finish("p")
+        return lg
+    ms = _time(lambda: prefill(tokens), args.warmup, args.steps)
+    out.update(value=round(tokens / ms * 1e3, 1), ms_per_step=round(ms, 3))
+    ms_p = _time(lambda: prefill(512), 1, max(1, args.steps // 2))
+    out["prefill_portions_512"] = {"tokens_per_s": round(tokens / ms_p * 1e3, 1), "ms": round(ms_p, 3)}
+
+    # ---- decode: 4 live requests with `ctx` tokens each, one token per request per step
+    ctx = 2048
+    s = Scheduler(model, max_tokens=4 * (ctx + 256), max_requests=4)
+    for r in range(4):
+        s.step([(r, prompt[:ctx], [])])
+    nxt = [[1], [2], [3], [4]]
+    ms_d = _time(lambda: s.step([(r, nxt[r], [0]) for r in range(4)]), args.warmup, 16)
+    out["decode"] = {"live_requests": 4, "context": ctx, "tokens_per_s": round(4 / ms_d * 1e3, 1), "ms_per_step": round(ms_d, 3)}
+    out["gpu_launches"] = ops.total_launches() - launches0
+
+    # ---- end to end through the generation entry point: pinned host tables in, sampled ids out every step
+    s = Scheduler(model, max_tokens=tokens + 256, max_requests=4)
+    t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    torch.cuda.synchronize()
+    t0.record()
+    gen = s.generate([prompt], max_new_tokens=8, step_tokens=tokens)
+    t1.record()
+    torch.cuda.synchronize()
+    out["e2e"] = {"value": round((tokens + 8) / t0.elapsed_time(t1) * 1e3, 1), "unit": "tokens/s (prompt + 8 generated, Scheduler.generate)",
+                  "h2d_bytes_per_step": s.h2d_bytes // max(s.steps_run, 1), "d2h_bytes_per_step": 8}
+
+    # ---- per-mixer times beside the closest blocks of the MoE prefill models at equal size
+    mix = {}
+    W = cfg.width
+    h = (torch.randn(tokens, W, generator=g) * 0.5).to(torch.bfloat16).to(dev)
+    tb = ops.StepTables([(prompt, 0, 0, list(range((tokens + 63) // 64)))], dev)
+    model.make_caches(tokens + 64, 4)
+    dl = model.layers[0]["mixer"]
+    tail, state = model._run_state[0]
+    mix["delta_mixer_ms"] = round(_time(lambda: dl.forward(h, tb, tail, state), 2, 5), 3)
+    la = model.layers[2]["mixer"]
+    ckv, kr = model.kv_cache.get_layer_caches(0)
+    mix["latent_attention_window_1024_ms"] = round(_time(lambda: la.forward(h, tb, ckv, kr, 64), 1, 3), 3)
+    try:
+        from types import SimpleNamespace
+        from .build import build
+        build()
+        from .attention import GatedDeltaNetAttention, MLAAttention, MLAPagedKVCache, SequenceKVState
+        from .model import SyntheticWeights, HybridMoEConfig
+        hc = HybridMoEConfig(hidden_size=W, linear_num_key_heads=16, linear_num_value_heads=32, linear_key_head_dim=128,
+                             linear_value_head_dim=128, linear_conv_kernel_dim=4, num_attention_heads=16, kv_lora_rank=512,
+                             qk_nope_head_dim=128, qk_rope_head_dim=64, v_head_dim=128, rope_theta=10000.0, rms_norm_eps=1e-5)
+        src = SyntheticWeights(hc, dev, 0)
+        ac = SimpleNamespace(**{f: getattr(hc, f) for f in hc.__dataclass_fields__})
+        gdn = GatedDeltaNetAttention(ac, 0, src.attention(0, "linear_attention"), dev, max_tokens=tokens)
+
+        def gdn_step():
+            gdn.reset_state()
+            gdn.forward(h)
+        mix["gated_deltanet_block_ms"] = round(_time(gdn_step, 2, 5), 3)
+        mla = MLAAttention(ac, 0, src.attention(0, "mla"), dev, max_tokens=tokens, max_kv_len=tokens)
+        kv = MLAPagedKVCache(1, 512, 64, dev, max_pages=tokens // 16 + 2)
+        pos = torch.arange(tokens, dtype=torch.int32, device=dev)
+
+        def mla_step():
+            st = SequenceKVState(kv)
+            mla.forward(h, pos, kv, st, 0, num_new_tokens=tokens)
+            st.free()
+        mix["mla_block_full_causal_ms"] = round(_time(mla_step, 2, 5), 3)
+    except Exception as exc:       # noqa: BLE001 — the comparison is optional; the new design's numbers stand without it
+        mix["comparison_unavailable"] = f"{type(exc).__name__}: {exc}"
+    out["mixers_at_equal_size"] = mix
+    out["peaks"] = peaks
+    print(json.dumps(out))

@@ -71,7 +71,8 @@ def latent_attention(h, w, p, m, eps):
     T = h.shape[0]
     H, dn, dr, dv, r = m["heads"], m["dim"], m["rot_dim"], m["vdim"], m["kv_rank"]
     pos = np.arange(T, dtype=np.float64)
-    freq, amp = yarn_frequencies(m["rot"]["dims"], m["rot"]["base"], m["rot"].get("scaling"))
+    rot = m.get("rot") or {}
+    freq, amp = yarn_frequencies(rot.get("dims", 0), rot.get("base", 10000.0), rot.get("scaling")) if rot.get("dims", 0) else (np.zeros(0), 1.0)
     q = (h @ w["q"].T).reshape(T, H, dn + dr)
     dkv = h @ w["dkv"].T
     c = rms_norm(dkv[:, :r], w["dkv.norm"], eps)
@@ -80,7 +81,7 @@ def latent_attention(h, w, p, m, eps):
     k_nope = (c @ w["uk"].T).reshape(T, H, dn)
     v = (c @ w["uv"].T).reshape(T, H, dv)
     out = np.zeros((T, H, dv))
-    win = m["mask"]["size"]
+    win = (m.get("mask") or {}).get("size") or T + 1          # no mask: every earlier position is seen
     for hd in range(H):
         s = (q[:, hd, :dn] @ k_nope[:, hd].T + q_rot[hd] @ k_rot.T) * m["scale"]
         i, j = np.arange(T)[:, None], np.arange(T)[None, :]
@@ -161,7 +162,7 @@ def layer_schedule(cfg):
 
 def forward(cfg, weights, tokens, return_layers=False):
     """Logits [T, vocab] of one whole sequence (and the residual stream after every layer run)."""
-    W = {k: np.asarray(v, dtype=np.float64) for k, v in weights.items() if k != "side.embed" or True}
+    W = {k: np.asarray(v, dtype=np.float64) for k, v in weights.items()}
     tokens = np.asarray(tokens, dtype=np.int64)
     eps = cfg["norm"]["eps"]
     x0 = W["embed"][tokens] * cfg["embedding"]["scale"]
