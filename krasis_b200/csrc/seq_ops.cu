@@ -184,10 +184,72 @@ __global__ void __launch_bounds__(256) gemv_nt_kernel(const TA* __restrict__ A, 
   }
 }
 
+// bf16 weights, K a multiple of 8, 16-byte aligned rows: a lane reads 8 weights per load
+__device__ __forceinline__ void unpack8(const uint4& v, float* f) {
+  const __nv_bfloat162* p = reinterpret_cast<const __nv_bfloat162*>(&v);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const float2 t = __bfloat1622float2(p[i]);
+    f[2 * i] = t.x;
+    f[2 * i + 1] = t.y;
+  }
+}
+template <typename TA> __device__ __forceinline__ void load8(const TA* p, float* f);
+template <> __device__ __forceinline__ void load8<float>(const float* p, float* f) {
+  const float4 a = *reinterpret_cast<const float4*>(p), b = *reinterpret_cast<const float4*>(p + 4);
+  f[0] = a.x; f[1] = a.y; f[2] = a.z; f[3] = a.w; f[4] = b.x; f[5] = b.y; f[6] = b.z; f[7] = b.w;
+}
+template <> __device__ __forceinline__ void load8<bf16>(const bf16* p, float* f) { unpack8(*reinterpret_cast<const uint4*>(p), f); }
+
+template <typename TA, typename TC, int MR>
+__global__ void __launch_bounds__(256) gemv_nt_vec_kernel(const TA* __restrict__ A, long long lda, const bf16* __restrict__ B, long long ldb,
+                                                          TC* __restrict__ C, long long ldc, int M, int N, int K, long long sA,
+                                                          long long sB, long long sC) {
+  A += (long long)blockIdx.z * sA;
+  B += (long long)blockIdx.z * sB;
+  C += (long long)blockIdx.z * sC;
+  const int lane = threadIdx.x & 31;
+  const int n = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (n >= N) return;
+  float acc[MR];
+#pragma unroll
+  for (int m = 0; m < MR; ++m) acc[m] = 0.f;
+  const bf16* b = B + (long long)n * ldb;
+  for (int k = lane * 8; k < K; k += 256) {
+    float w[8], a[8];
+    unpack8(*reinterpret_cast<const uint4*>(b + k), w);
+#pragma unroll
+    for (int m = 0; m < MR; ++m)
+      if (m < M) {
+        load8<TA>(A + (long long)m * lda + k, a);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) acc[m] = fmaf(a[i], w[i], acc[m]);
+      }
+  }
+#pragma unroll
+  for (int m = 0; m < MR; ++m) {
+    const float v = warp_sum(acc[m]);
+    if (lane == 0 && m < M) stf(C, (long long)m * ldc + n, v);
+  }
+}
+
+template <typename TA, typename TC>
+static bool launch_gemv_vec(const void* A, long long lda, const void* B, long long ldb, void* C, long long ldc, int M, int N, int K,
+                            int batch, long long sA, long long sB, long long sC, cudaStream_t s) {
+  const bool a16 = sizeof(TA) == 2;
+  if (K % 8 || ldb % 8 || sB % 8 || ((uintptr_t)B & 15) || ((uintptr_t)A & 15) || lda % (a16 ? 8 : 4) || sA % (a16 ? 8 : 4)) return false;
+  dim3 grid((N + 7) / 8, 1, batch);
+  gemv_nt_vec_kernel<TA, TC, 8><<<grid, 256, 0, s>>>((const TA*)A, lda, (const bf16*)B, ldb, (TC*)C, ldc, M, N, K, sA, sB, sC);
+  return true;
+}
+
 template <typename TA, typename TB, typename TC>
 static void launch_gemm(const void* A, long long lda, const void* B, long long ldb, void* C, long long ldc, int M, int N, int K,
                         int batch, long long sA, long long sB, long long sC, cudaStream_t s) {
   if (M <= 8) {
+    if constexpr (sizeof(TB) == 2) {
+      if (launch_gemv_vec<TA, TC>(A, lda, B, ldb, C, ldc, M, N, K, batch, sA, sB, sC, s)) return;
+    }
     dim3 grid((N + 7) / 8, 1, batch);
     gemv_nt_kernel<TA, TB, TC, 8><<<grid, 256, 0, s>>>((const TA*)A, lda, (const TB*)B, ldb, (TC*)C, ldc, M, N, K, sA, sB, sC);
   } else {
@@ -350,7 +412,8 @@ __global__ void __launch_bounds__(kAttnThreads) latent_window_attn_kernel(
   float* qs = sm + 2 * KT;                // [HG][D]
   float* kt = qs + HG * D;                // [KT][DP]
   float* pr = kt + KT * DP;               // [HG][KT]
-  float* m_run = pr + HG * KT;            // [HG]
+  float* sp = pr + HG * KT;               // [warps][KT] partial scores: a head's dot product is cut into warps / HG pieces
+  float* m_run = sp + (kAttnThreads / 32) * KT;   // [HG]
   float* l_run = m_run + HG;              // [HG]
   float* alpha = l_run + HG;              // [HG]
   const long long t = blockIdx.x;
@@ -378,26 +441,49 @@ __global__ void __launch_bounds__(kAttnThreads) latent_window_attn_kernel(
       krow[tid] = (long long)pages[(long long)seq * max_pages + j / page_size] * page_size + j % page_size;
     }
     __syncthreads();
-    for (int i = tid; i < nk * D; i += kAttnThreads) {
-      const int k = i / D, d = i - k * D;
-      kt[k * DP + d] = d < r ? ld_dt(ckv, dt_cache, krow[k] * r + d) : ld_dt(kr, dt_cache, krow[k] * dr + (d - r));
+    if (dt_cache == 1 && (r & 7) == 0 && (dr & 7) == 0) {
+      const int D8 = D >> 3;
+      for (int i = tid; i < nk * D8; i += kAttnThreads) {
+        const int k = i / D8, d = (i - k * D8) << 3;
+        const bf16* src = d < r ? (const bf16*)ckv + krow[k] * r + d : (const bf16*)kr + krow[k] * dr + (d - r);
+        float f[8];
+        unpack8(*reinterpret_cast<const uint4*>(src), f);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) kt[k * DP + d + e] = f[e];
+      }
+    } else {
+      for (int i = tid; i < nk * D; i += kAttnThreads) {
+        const int k = i / D, d = i - k * D;
+        kt[k * DP + d] = d < r ? ld_dt(ckv, dt_cache, krow[k] * r + d) : ld_dt(kr, dt_cache, krow[k] * dr + (d - r));
+      }
     }
     __syncthreads();
-    // scores and the running softmax: a warp per head, a lane per key
+    // scores: warp w takes piece w / HG of head w % HG, a lane per key (HG is a power of two <= 8, KT == 32)
+    {
+      const int P = (kAttnThreads / 32) / HG, part = warp / HG, hw = warp % HG;
+      const int dseg = (D + P - 1) / P, d_lo = part * dseg, d_hi = min(D, d_lo + dseg);
+      float dot = 0.f;
+      if (hw < nh && lane < nk) {
+        const float* qh = qs + hw * D;
+        const float* kk = kt + lane * DP;
+        for (int d = d_lo; d < d_hi; ++d) dot = fmaf(qh[d], kk[d], dot);
+      }
+      sp[warp * KT + lane] = dot;
+    }
+    __syncthreads();
+    // running softmax: warp hh < nh
     for (int hh = warp; hh < nh; hh += kAttnThreads / 32) {
-      const float* qh = qs + hh * D;
       const float m_old = m_run[hh];
       float m_new = m_old;
-      for (int kb = 0; kb < nk; kb += 32) {
-        const int k = kb + lane;
+      {
+        const int P = (kAttnThreads / 32) / HG;
         float sc = -INFINITY;
-        if (k < nk) {
-          const float* kk = kt + k * DP;
+        if (lane < nk) {
           float dot = 0.f;
-          for (int d = 0; d < D; ++d) dot = fmaf(qh[d], kk[d], dot);
+          for (int pp = 0; pp < P; ++pp) dot += sp[(pp * HG + hh) * KT + lane];
           sc = dot * scale;
         }
-        if (k < KT) pr[hh * KT + k] = sc;
+        pr[hh * KT + lane] = sc;
         m_new = fmaxf(m_new, warp_max(sc));
       }
       float lsum = 0.f;
@@ -561,6 +647,168 @@ __global__ void __launch_bounds__(1024) delta_rule_kernel(const float* __restric
   for (int i = tid; i < dk * dv; i += blockDim.x) Sg[i] = S[i];
 }
 
+
+// ---- the same recurrence for key sizes 32 / 64 / 128 and value sizes that are multiples of 32: state in registers.
+// delta_prep: unit-norm q (times dk^-1/2) and k per (token, key head), write strength and decay per (token, head), all tokens in
+// parallel.  delta_rule_reg: one block per (sequence, head, 32 value columns); a column's DK state entries live in the registers of
+// four adjacent lanes (DK / 4 each), the two dot products per token are finished with two shuffles; q / k / v / gates of the next 16
+// tokens stream into shared memory with cp.async while the current 16 are processed.  delta_out: per-head RMS norm and SiLU gate.
+__global__ void __launch_bounds__(256) delta_prep_kernel(const float* __restrict__ conv, int C, const float* __restrict__ proj,
+                                                         long long ldp, int a_off, int b_off, int H, int Hk, int dk,
+                                                         const float* __restrict__ A_log, const float* __restrict__ dt_bias, long long T,
+                                                         float* __restrict__ qn, float* __restrict__ kn, float* __restrict__ beta,
+                                                         float* __restrict__ dec) {
+  const long long w = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  const int lane = threadIdx.x & 31;
+  if (w >= T * Hk) return;
+  const long long t = w / Hk;
+  const int hk = (int)(w - t * Hk);
+  const float* row = conv + t * C;
+  const int q_col = hk * dk, k_col = Hk * dk + hk * dk;
+  float sq = 0.f, sk = 0.f;
+  for (int i = lane; i < dk; i += 32) {
+    const float qv = row[q_col + i], kv = row[k_col + i];
+    sq += qv * qv;
+    sk += kv * kv;
+  }
+  sq = warp_sum(sq);
+  sk = warp_sum(sk);
+  const float rq = rsqrtf((float)dk) / sqrtf(sq + 1e-6f), rk = 1.f / sqrtf(sk + 1e-6f);
+  for (int i = lane; i < dk; i += 32) {
+    qn[w * dk + i] = row[q_col + i] * rq;
+    kn[w * dk + i] = row[k_col + i] * rk;
+  }
+  const int rep = H / Hk;
+  if (lane < rep) {
+    const int h = hk * rep + lane;
+    const float* pr = proj + t * ldp;
+    beta[t * H + h] = 1.f / (1.f + expf(-pr[b_off + h]));
+    dec[t * H + h] = expf(-expf(A_log[h]) * softplus(pr[a_off + h] + dt_bias[h]));
+  }
+}
+
+__device__ __forceinline__ void cp_async16(void* smem_dst, const void* gmem_src) {
+  asm volatile("cp.async.ca.shared.global [%0], [%1], 16;" ::"r"((uint32_t)__cvta_generic_to_shared(smem_dst)), "l"(gmem_src) : "memory");
+}
+__device__ __forceinline__ void cp_async4(void* smem_dst, const void* gmem_src) {
+  asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"((uint32_t)__cvta_generic_to_shared(smem_dst)), "l"(gmem_src) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+__device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_group 0;" ::: "memory"); }
+
+constexpr int kRegTile = 16;
+template <int DK>
+__global__ void __launch_bounds__(128) delta_rule_reg_kernel(const float* __restrict__ qn, const float* __restrict__ kn,
+                                                             const float* __restrict__ conv, int C, int v_col0,
+                                                             const float* __restrict__ beta, const float* __restrict__ dec, int H, int Hk,
+                                                             int dv, float* __restrict__ state, const int* __restrict__ cu,
+                                                             const int* __restrict__ slots, float* __restrict__ o_out) {
+  constexpr int Q = DK / 4;                 // state rows per lane
+  constexpr int RS = 4 * (Q + 4);           // padded q / k row in shared memory: the four quarters land in different banks
+  __shared__ __align__(16) float ks[2][kRegTile][RS];
+  __shared__ __align__(16) float qs[2][kRegTile][RS];
+  __shared__ __align__(16) float vs[2][kRegTile][32];
+  __shared__ float bs[2][kRegTile], gs[2][kRegTile];
+  __shared__ float os[kRegTile][33];
+  const int s = blockIdx.x, h = blockIdx.y, j0 = blockIdx.z * 32;
+  const int hk = h / (H / Hk);
+  const int tid = threadIdx.x, quarter = tid & 3, col = tid >> 2;
+  const int t0 = cu[s], n = cu[s + 1] - cu[s];
+  float* Sg = state + ((long long)slots[s] * H + h) * DK * dv;
+  float S[Q];
+#pragma unroll
+  for (int ii = 0; ii < Q; ++ii) S[ii] = Sg[(long long)(quarter * Q + ii) * dv + j0 + col];
+
+  auto load_tile = [&](int buf, int b0) {
+    const int nt = min(kRegTile, n - b0);
+    for (int c = tid; c < nt * (DK / 4); c += 128) {                 // 16-byte chunks of the q and k rows
+      const int tt = c / (DK / 4), cc = c - tt * (DK / 4);
+      const int dst = (cc / (Q / 4)) * (Q + 4) + (cc % (Q / 4)) * 4;
+      const long long src = ((long long)(t0 + b0 + tt) * Hk + hk) * DK + cc * 4;
+      cp_async16(&ks[buf][tt][dst], kn + src);
+      cp_async16(&qs[buf][tt][dst], qn + src);
+    }
+    for (int c = tid; c < nt * 8; c += 128) {
+      const int tt = c >> 3, cc = c & 7;
+      cp_async16(&vs[buf][tt][cc * 4], conv + (long long)(t0 + b0 + tt) * C + v_col0 + h * dv + j0 + cc * 4);
+    }
+    if (tid < nt) {
+      cp_async4(&bs[buf][tid], beta + (long long)(t0 + b0 + tid) * H + h);
+      cp_async4(&gs[buf][tid], dec + (long long)(t0 + b0 + tid) * H + h);
+    }
+    cp_async_commit();
+  };
+
+  load_tile(0, 0);
+  int buf = 0;
+  for (int b0 = 0; b0 < n; b0 += kRegTile, buf ^= 1) {
+    const int nt = min(kRegTile, n - b0);
+    cp_async_wait_all();
+    __syncthreads();                                  // tile `buf` is in place; everyone is done with the other buffer and with os
+    if (b0 + kRegTile < n) load_tile(buf ^ 1, b0 + kRegTile);
+    for (int tt = 0; tt < nt; ++tt) {
+      const float g = gs[buf][tt], b = bs[buf][tt];
+      const float4* k4 = reinterpret_cast<const float4*>(&ks[buf][tt][quarter * (Q + 4)]);
+      const float4* q4 = reinterpret_cast<const float4*>(&qs[buf][tt][quarter * (Q + 4)]);
+      float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
+#pragma unroll
+      for (int ii = 0; ii < Q / 4; ++ii) {
+        const float4 kk = k4[ii];
+        a0 = fmaf(S[4 * ii], kk.x, a0);
+        a1 = fmaf(S[4 * ii + 1], kk.y, a1);
+        a2 = fmaf(S[4 * ii + 2], kk.z, a2);
+        a3 = fmaf(S[4 * ii + 3], kk.w, a3);
+      }
+      float sk = (a0 + a1) + (a2 + a3);
+      sk += __shfl_xor_sync(0xffffffffu, sk, 1);
+      sk += __shfl_xor_sync(0xffffffffu, sk, 2);
+      const float u = b * (vs[buf][tt][col] - g * sk);
+      a0 = a1 = a2 = a3 = 0.f;
+#pragma unroll
+      for (int ii = 0; ii < Q / 4; ++ii) {
+        const float4 kk = k4[ii], qq = q4[ii];
+        S[4 * ii] = fmaf(kk.x, u, g * S[4 * ii]);
+        S[4 * ii + 1] = fmaf(kk.y, u, g * S[4 * ii + 1]);
+        S[4 * ii + 2] = fmaf(kk.z, u, g * S[4 * ii + 2]);
+        S[4 * ii + 3] = fmaf(kk.w, u, g * S[4 * ii + 3]);
+        a0 = fmaf(S[4 * ii], qq.x, a0);
+        a1 = fmaf(S[4 * ii + 1], qq.y, a1);
+        a2 = fmaf(S[4 * ii + 2], qq.z, a2);
+        a3 = fmaf(S[4 * ii + 3], qq.w, a3);
+      }
+      float o = (a0 + a1) + (a2 + a3);
+      o += __shfl_xor_sync(0xffffffffu, o, 1);
+      o += __shfl_xor_sync(0xffffffffu, o, 2);
+      if (quarter == 0) os[tt][col] = o;
+    }
+    __syncthreads();
+    for (int i = tid; i < nt * 32; i += 128) {
+      const int tt = i >> 5, c = i & 31;
+      o_out[((long long)(t0 + b0 + tt) * H + h) * dv + j0 + c] = os[tt][c];
+    }
+  }
+#pragma unroll
+  for (int ii = 0; ii < Q; ++ii) Sg[(long long)(quarter * Q + ii) * dv + j0 + col] = S[ii];
+}
+
+// out[t, h, :] = o / rms(o) * norm_w * silu(gate); a warp per (token, head)
+__global__ void __launch_bounds__(256) delta_out_kernel(const float* __restrict__ o, const float* __restrict__ proj, long long ldp, int g_off,
+                                                        int H, int dv, const float* __restrict__ norm_w, float eps, long long T,
+                                                        void* __restrict__ out, int dt_out) {
+  const long long w = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  const int lane = threadIdx.x & 31;
+  if (w >= T * H) return;
+  const long long t = w / H;
+  const int h = (int)(w - t * H);
+  const float* row = o + w * dv;
+  float ss = 0.f;
+  for (int j = lane; j < dv; j += 32) ss += row[j] * row[j];
+  ss = warp_sum(ss);
+  const float rstd = 1.f / sqrtf(ss / (float)dv + eps);
+  for (int j = lane; j < dv; j += 32)
+    st_dt(out, dt_out, w * dv + j, row[j] * rstd * norm_w[j] * silu(proj[t * ldp + g_off + h * dv + j]));
+}
+
 }  // namespace kb2seq
 
 using namespace kb2seq;
@@ -654,13 +902,13 @@ KB2SEQ_API int kb2_seq_latent_window_attn(const float* q_abs, const float* proj,
       window <= 0 || bad_dt(dt_cache))
     return failf(KB2SEQ_ERR_VALUE, "latent_window_attn: bad argument");
   if (r > kAttnThreads * kAttnAcc) return failf(KB2SEQ_ERR_VALUE, "latent_window_attn: latent size %d > %d", r, kAttnThreads * kAttnAcc);
-  int HG = kAttnThreads * kAttnAcc / r;
-  if (HG > H) HG = H;
-  if (HG > 8) HG = 8;
+  int HG = 8;                              // heads per block: a power of two, so that the 8 warps split evenly over the heads
+  while (HG > 1 && (HG > H || HG * r > kAttnThreads * kAttnAcc)) HG >>= 1;
   const int D = r + dr;
-  int KT = 32;
-  auto smem_of = [&](int hg, int kt) { return (size_t)(hg * D + kt * (D + 1) + hg * kt + 3 * hg) * 4 + (size_t)kt * 8; };
-  while (HG > 1 && smem_of(HG, KT) > 200 * 1024) --HG;
+  const int KT = 32;
+  auto smem_of = [&](int hg, int kt) { return (size_t)(hg * D + kt * (D + 1) + hg * kt + 8 * kt + 3 * hg) * 4 + (size_t)kt * 8; };
+  while (HG > 1 && smem_of(HG, KT) > 200 * 1024) HG >>= 1;
+  while (HG > 1 && (long long)T * ((H + HG - 1) / HG) < 296) HG >>= 1;     // few tokens (decode): more blocks, finer pieces
   const size_t smem = smem_of(HG, KT);
   if (smem > 200 * 1024) return failf(KB2SEQ_ERR_VALUE, "latent_window_attn: latent + rotated size %d too large", D);
   if (smem > 48 * 1024) SEQ_CUDA(cudaFuncSetAttribute(latent_window_attn_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
@@ -687,12 +935,36 @@ KB2SEQ_API int kb2_seq_conv_silu(const float* proj, long long ldp, int T, int S,
   return KB2SEQ_OK;
 }
 
-KB2SEQ_API int kb2_seq_delta_rule(const float* conv, int C, const float* proj, long long ldp, int g_off, int a_off, int b_off, int S,
-                                  int H, int Hk, int dk, int dv, const float* A_log, const float* dt_bias, const float* norm_w, float eps,
-                                  float* state, const int* cu, const int* slots, void* out, int dt_out, void* stream) {
+KB2SEQ_API int kb2_seq_delta_rule(const float* conv, int C, const float* proj, long long ldp, int g_off, int a_off, int b_off, int T,
+                                  int S, int H, int Hk, int dk, int dv, const float* A_log, const float* dt_bias, const float* norm_w,
+                                  float eps, float* state, const int* cu, const int* slots, float* scratch, void* out, int dt_out,
+                                  void* stream) {
   if (!conv || !proj || !A_log || !dt_bias || !norm_w || !state || !cu || !slots || !out || S <= 0 || H <= 0 || Hk <= 0 || H % Hk ||
       dk <= 0 || dv <= 0 || bad_dt(dt_out))
     return failf(KB2SEQ_ERR_VALUE, "delta_rule: bad argument");
+  if (scratch && (dk == 32 || dk == 64 || dk == 128) && dv % 32 == 0 && C % 4 == 0 && ((2 * Hk * dk) % 4) == 0) {
+    // scratch: qn [T, Hk, dk] | kn [T, Hk, dk] | beta [T, H] | dec [T, H] | o [T, H, dv]   (fp32)
+    cudaStream_t st = (cudaStream_t)stream;
+    float* qn = scratch;
+    float* kn = qn + (long long)T * Hk * dk;
+    float* be = kn + (long long)T * Hk * dk;
+    float* de = be + (long long)T * H;
+    float* ob = de + (long long)T * H;
+    if ((((long long)T * Hk * dk) | ((long long)T * H)) % 4) ob = (float*)(((uintptr_t)ob + 15) & ~(uintptr_t)15);
+    const long long nw = (long long)T * Hk;
+    delta_prep_kernel<<<(unsigned)((nw + 7) / 8), 256, 0, st>>>(conv, C, proj, ldp, a_off, b_off, H, Hk, dk, A_log, dt_bias, T, qn, kn, be, de);
+    SEQ_LAUNCHED();
+    dim3 grid(S, H, dv / 32);
+    const int v_col0 = 2 * Hk * dk;
+    if (dk == 32) delta_rule_reg_kernel<32><<<grid, 128, 0, st>>>(qn, kn, conv, C, v_col0, be, de, H, Hk, dv, state, cu, slots, ob);
+    else if (dk == 64) delta_rule_reg_kernel<64><<<grid, 128, 0, st>>>(qn, kn, conv, C, v_col0, be, de, H, Hk, dv, state, cu, slots, ob);
+    else delta_rule_reg_kernel<128><<<grid, 128, 0, st>>>(qn, kn, conv, C, v_col0, be, de, H, Hk, dv, state, cu, slots, ob);
+    SEQ_LAUNCHED();
+    const long long no = (long long)T * H;
+    delta_out_kernel<<<(unsigned)((no + 7) / 8), 256, 0, st>>>(ob, proj, ldp, g_off, H, dv, norm_w, eps, T, out, dt_out);
+    SEQ_LAUNCHED();
+    return KB2SEQ_OK;
+  }
   if (dv > 1024) return failf(KB2SEQ_ERR_VALUE, "delta_rule: value size %d > 1024", dv);
   const size_t smem = ((size_t)dk * dv + (size_t)kDeltaTile * (2 * dk + dv + 2)) * 4;
   if (smem > 220 * 1024) return failf(KB2SEQ_ERR_VALUE, "delta_rule: a %d x %d state does not fit one block's shared memory", dk, dv);

@@ -137,6 +137,8 @@ class GatedDeltaMixer:
         self.taps = f(torch.cat([weights["q_conv"], weights["k_conv"], weights["v_conv"]], 0))
         self.A_log, self.dt_bias, self.norm = f(weights["A_log"]), f(weights["dt_bias"]), f(weights["norm"])
         self.w_o = d(weights["o"])
+        # key sizes 32 / 64 / 128 with value sizes that are multiples of 32 keep the state in registers; others in shared memory
+        self.register_state_kernel = dim in (32, 64, 128) and vdim % 32 == 0
 
     def register_state(self, pool):
         """(conv tail [slots, C, taps - 1], recurrent state [slots, H, dk, dv]) in a RecurrentStatePool."""
@@ -150,10 +152,13 @@ class GatedDeltaMixer:
         ops.check(lib.kb2_seq_conv_silu(proj.data_ptr(), proj.stride(0), T, tb.S, self.C, self.K, self.taps.data_ptr(), tail.data_ptr(),
                                         tb.seq_of.data_ptr(), tb.cu.data_ptr(), tb.slots.data_ptr(), conv.data_ptr(), s))
         o = torch.empty((T, self.H * self.dv), dtype=self.dtype, device=h.device)
-        ops.check(lib.kb2_seq_delta_rule(conv.data_ptr(), self.C, proj.data_ptr(), proj.stride(0), self.g_off, self.a_off, self.b_off,
+        scratch = None
+        if self.register_state_kernel:
+            scratch = torch.empty(2 * T * self.Hk * self.dk + 2 * T * self.H + T * self.H * self.dv + 4, dtype=torch.float32, device=h.device)
+        ops.check(lib.kb2_seq_delta_rule(conv.data_ptr(), self.C, proj.data_ptr(), proj.stride(0), self.g_off, self.a_off, self.b_off, T,
                                          tb.S, self.H, self.Hk, self.dk, self.dv, self.A_log.data_ptr(), self.dt_bias.data_ptr(),
                                          self.norm.data_ptr(), self.eps, state.data_ptr(), tb.cu.data_ptr(), tb.slots.data_ptr(),
-                                         o.data_ptr(), ops.dt_code(self.dtype), s))
+                                         scratch.data_ptr() if scratch is not None else None, o.data_ptr(), ops.dt_code(self.dtype), s))
         return lin(o, self.w_o, torch.float32)
 
 

@@ -193,7 +193,10 @@ def test_latent_attention_alone(seq, mixer):
 
 
 @pytest.mark.parametrize("mixer", [delta_cfg(), delta_cfg(heads=1, kv_heads=1, dim=8, vdim=8, conv=1), delta_cfg(heads=6, kv_heads=2, dim=40, vdim=24, conv=3),
-                                   delta_cfg(heads=2, kv_heads=2, dim=16, vdim=72, conv=5)])
+                                   delta_cfg(heads=2, kv_heads=2, dim=16, vdim=72, conv=5),
+                                   # key sizes 32 / 64 / 128 with value sizes in multiples of 32 run the register-state kernels
+                                   delta_cfg(heads=2, kv_heads=1, dim=32, vdim=32, conv=3), delta_cfg(heads=3, kv_heads=3, dim=64, vdim=64, conv=4),
+                                   delta_cfg(heads=2, kv_heads=2, dim=128, vdim=96, conv=2)])
 def test_delta_mixer_alone(seq, mixer):
     raw = _one_layer("delta", mixer)
     model, w = build(raw, seed=12)
@@ -203,6 +206,20 @@ def test_delta_mixer_alone(seq, mixer):
     close(run_portions(model, tk, [T]), want, 3e-5, "delta, whole prompt")
     close(run_portions(model, tk, [17, 2, 3, 1, 30]), want, 3e-5, "delta, portions and decoding")
     close(run_portions(model, tk, []), want, 3e-5, "delta, token by token")
+
+
+def test_latent_attention_bfloat16_cache_and_decode_grids(seq):
+    """bf16 cache rows read 8 values at a time (latent and rotated sizes in multiples of 8); a step of few tokens runs one head per
+    block with the dot products cut into pieces, a long portion runs 8 heads per block: both against the oracle and each other."""
+    raw = _one_layer("latent_attention", latent_cfg(heads=16, dim=16, rot_dim=8, vdim=16, kv_rank=64, window=40), width=64)
+    tk = toks(120, raw["vocab"], 15)
+    for dtype, tol in ((torch.float32, 3e-5), (torch.bfloat16, 4e-2)):
+        model, w = build(raw, dtype=dtype, seed=14)
+        want = O.forward(raw, w, tk)
+        a = run_portions(model, tk, [120])
+        b = run_portions(model, tk, [100])           # 100 at once (8 heads per block), then 20 single tokens (1 head per block)
+        close(a, want, tol, f"{dtype} whole")
+        close(b, want, tol, f"{dtype} portion + decoding")
 
 
 def test_mlp_and_side_alone(seq):
