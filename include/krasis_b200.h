@@ -347,6 +347,14 @@ KB2_API int kb2_mla_forward(kb2_mla* h, int layer, const void* hidden_dev, const
                             void* ckv_cache_layer_dev, void* kpe_cache_layer_dev, const int32_t* kv_indices_dev,
                             int32_t kv_len_after, void* out_dev, int32_t num_tokens, void* stream);
 
+/* The MLA attention core alone on dense BF16 rows, for callers with a cache of their own (ragged-batch serving):
+ * q [M][nh*192] (per head 128 unrotated + 64 rotated dims, rotation applied), kv_up [kv_len][nh*256] = [k_nope of all heads | v of all
+ * heads], kpe [kv_len][64], out [M][nh*128].  Query i stands at row q_start + i of the kv rows (kv_len == q_start + M) and sees the
+ * keys with 0 <= position - key < window; sinks (fp32 [nh], may be NULL) adds exp(sink_h) to head h's softmax denominator. */
+KB2_API int kb2_fmha_latent(const void* q_dev, const void* kv_up_dev, const void* kpe_dev, void* out_dev, int32_t M, int32_t q_start,
+                            int32_t kv_len, int32_t num_heads, float sm_scale, int32_t window, const float* sinks_dev, int32_t device,
+                            void* stream);
+
 /* GEMM -> reduce-scatter fused (head-parallel attention under token sharding): after kb2_{gdn,gqa,mla}_set_output_scatter the
  * block's out_proj GEMM stores every output row straight into the receive buffer of the rank that owns the token
  * (peer_recv_host[r] from kb2_comm_peer_alloc, layout [M / num_ranks][num_ranks][hidden] bf16, slot = src_rank) instead of out_dev

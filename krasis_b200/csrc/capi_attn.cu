@@ -43,6 +43,8 @@ cudaError_t launch_gqa_core(const GqaDims& g, const void* q_raw, const void* k_r
                             const float* k_norm, const int* positions, const int* kv_indices, void* q_rot, void* k_cache,
                             void* v_cache, void* k_bf, void* v_bf, void* attn_out, int M, int q_start, int kv_len,
                             cudaStream_t s);
+cudaError_t launch_fmha_latent(const void* q, const void* kv_up, const void* kpe, void* out, int M, int q_start, int kv_len, int nh,
+                               float sm_scale, int window, const float* sinks, cudaStream_t s);
 struct MlaDims {
   int H, nh, nope, rope, dv, lora;
   float eps;
@@ -625,6 +627,18 @@ KB2_API int kb2_mla_forward(kb2_mla* h, int layer, const void* hidden_dev, const
                            ckv_cache_layer_dev, kpe_cache_layer_dev, h->ckv_bf16, h->kpe_bf16, h->kv_up, h->attn, M,
                            first_position, kv_len_after, c.sm_scale, sms, s));
   CUDA_TRY(launch_dense_gemm_scatter(h->attn, L.wo, out_dev, nullptr, M, H, nh * 128, H, false, sms, s, scatter_for(h->out_scatter, M)));
+  return KB2_OK;
+}
+
+KB2_API int kb2_fmha_latent(const void* q_dev, const void* kv_up_dev, const void* kpe_dev, void* out_dev, int32_t M, int32_t q_start,
+                            int32_t kv_len, int32_t num_heads, float sm_scale, int32_t window, const float* sinks_dev, int32_t device,
+                            void* stream) {
+  if (!q_dev || !kv_up_dev || !kpe_dev || !out_dev) return failf(KB2_ERR_VALUE, "null argument");
+  if (M <= 0 || num_heads <= 0 || q_start < 0 || kv_len != q_start + M || window <= 0)
+    return failf(KB2_ERR_VALUE, "fmha_latent: need M > 0, kv_len == q_start + M, window > 0 (M=%d q_start=%d kv_len=%d)", M, q_start, kv_len);
+  CUDA_TRY(cudaSetDevice(device));
+  CUDA_TRY(launch_fmha_latent(q_dev, kv_up_dev, kpe_dev, out_dev, M, q_start, kv_len, num_heads, sm_scale, window, sinks_dev,
+                              (cudaStream_t)stream));
   return KB2_OK;
 }
 

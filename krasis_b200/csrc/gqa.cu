@@ -178,7 +178,9 @@ __global__ void __launch_bounds__(kFThreads, 1)
                     const __grid_constant__ CUtensorMap tmap_kpe, const __grid_constant__ CUtensorMap tmap_v, GqaDims g,
                     const __nv_bfloat16* __restrict__ q_raw,     // for the output gate (g.gated)
                     __nv_bfloat16* __restrict__ out,             // [M][nh*DV]
-                    int M, int q_start, int kv_len, float sm_scale_log2, int k_col0, int v_col0) {
+                    int M, int q_start, int kv_len, float sm_scale_log2, int k_col0, int v_col0,
+                    int window = 1 << 30,                        // a query sees the keys with 0 <= q_pos - key < window
+                    const float* __restrict__ sinks = nullptr) { // per head: exp(sink) joins the softmax denominator (no value)
   using L = FmhaSmem<DQ, DV>;
   constexpr int D = DQ;
   constexpr int NC = DQ / 64;                      // 64-wide d chunks of q/k
@@ -204,7 +206,10 @@ __global__ void __launch_bounds__(kFThreads, 1)
   // keys visible to this tile: positions <= q_start + min(q0 + 127, M - 1)
   const int last_q = min(q0 + kFQ - 1, M - 1);
   const int n_keys = min(kv_len, q_start + last_q + 1);
-  const int n_tiles = (n_keys + kFK - 1) / kFK;
+  // sliding window: the tile's first query needs no key before q_start + q0 - window + 1, so whole KV tiles below are skipped;
+  // every role counts tiles from tile0 (TMA coordinates and key positions add it back)
+  const int tile0 = max(0, q_start + q0 - window + 1) / kFK;
+  const int n_tiles = (n_keys + kFK - 1) / kFK - tile0;
 
   if (threadIdx.x == 128) {
     if (smem_u32(smem) & 1023u) __trap();
@@ -242,15 +247,15 @@ __global__ void __launch_bounds__(kFThreads, 1)
         if (elect_one()) {
           mbar_arrive_expect_tx(&k_full[stage], L::kKBytes);
 #pragma unroll
-          for (int c = 0; c < NKC; ++c) tma_load_2d(ks + c * (kFK * 128), &tmap_k, kx + c * 64, it * kFK, &k_full[stage]);
-          if constexpr (PE) tma_load_2d(ks + NKC * (kFK * 128), &tmap_kpe, 0, it * kFK, &k_full[stage]);
+          for (int c = 0; c < NKC; ++c) tma_load_2d(ks + c * (kFK * 128), &tmap_k, kx + c * 64, (it + tile0) * kFK, &k_full[stage]);
+          if constexpr (PE) tma_load_2d(ks + NKC * (kFK * 128), &tmap_kpe, 0, (it + tile0) * kFK, &k_full[stage]);
         }
         __syncwarp();
         mbar_wait(&v_empty[stage], phase ^ 1);
         if (elect_one()) {
           mbar_arrive_expect_tx(&v_full[stage], L::kVBytes);
 #pragma unroll
-          for (int c = 0; c < DV / 64; ++c) tma_load_2d(vs + c * (kFK * 128), &tmap_v, vx + c * 64, it * kFK, &v_full[stage]);
+          for (int c = 0; c < DV / 64; ++c) tma_load_2d(vs + c * (kFK * 128), &tmap_v, vx + c * 64, (it + tile0) * kFK, &v_full[stage]);
         }
         __syncwarp();
         if (++stage == kFStages) { stage = 0; phase ^= 1; }
@@ -375,12 +380,12 @@ __global__ void __launch_bounds__(kFThreads, 1)
       }
       tc_fence_before_sync();
       mbar_arrive(s_cons);                         // S may be overwritten by the next QK^T
-      const int key0 = it * kFK + hf * KH;
-      // causal / length mask only where a key of this half-tile can be invisible to a row of this warp (warp-uniform)
-      if (key0 + KH - 1 > q_start + q0 + q * 32 || key0 + KH > kv_len) {
+      const int key0 = (it + tile0) * kFK + hf * KH;
+      // causal / length / window mask only where a key of this half-tile can be invisible to a row of this warp (warp-uniform)
+      if (key0 + KH - 1 > q_start + q0 + q * 32 || key0 + KH > kv_len || key0 + window <= q_start + q0 + q * 32 + 31) {
 #pragma unroll
         for (int jj = 0; jj < KH; ++jj)
-          if (key0 + jj > q_pos || key0 + jj >= kv_len) s[jj] = -INFINITY;
+          if (key0 + jj > q_pos || key0 + jj >= kv_len || key0 + jj + window <= q_pos) s[jj] = -INFINITY;
       }
       float m_tile = -INFINITY;
 #pragma unroll
@@ -435,6 +440,7 @@ __global__ void __launch_bounds__(kFThreads, 1)
     }
     if (n_tiles > 0) {
       float* xb = xchg + (n_tiles & 1) * (2 * kFQ);   // the buffer the last tile did not use
+      if (sinks != nullptr && hf == 0 && m_ref != -INFINITY) l_sum += ex2_approx(fmaf(sinks[head], 1.4426950408889634f, -m_ref));
       xb[hf * kFQ + row] = l_sum;
       named_bar_sync(1 + q, 64);
       l_sum += xb[(hf ^ 1) * kFQ + row];
@@ -696,6 +702,35 @@ cudaError_t launch_mla_core(const MlaDims& m, void* q_full, const void* kv_a, co
   KernelSpan ks(K_FMHA, s);
   gqa_fmha_kernel<192, 128, true><<<grid, kFThreads, FmhaSmem<192, 128>::kTotal, s>>>(
       tq, tk, tpe, tk, g, nullptr, (__nv_bfloat16*)attn_out, M, q_start, kv_len, sl2, 0, m.nh * m.nope);
+  return cudaGetLastError();
+}
+
+// The attention core alone on dense BF16 rows, for callers that keep their own cache: q [M][nh*192] (per head 128 unrotated + 64
+// rotated), kv_up [kv_len][nh*256] = [k_nope of every head | v of every head], kpe [kv_len][64] (the rotated key part all heads share),
+// out [M][nh*128].  Query i stands at position q_start + i of the kv rows and sees the keys with 0 <= position - key < window;
+// sinks (fp32 [nh], may be null) adds exp(sink) to each head's softmax denominator.
+cudaError_t launch_fmha_latent(const void* q, const void* kv_up, const void* kpe, void* out, int M, int q_start, int kv_len, int nh,
+                               float sm_scale, int window, const float* sinks, cudaStream_t s) {
+  if (M <= 0 || nh <= 0 || q_start < 0 || kv_len != q_start + M || window <= 0) return cudaErrorInvalidValue;
+  static PerDeviceOnce once;
+  if (const int dev = once.pending(); dev >= 0) {
+    cudaError_t e0 = cudaFuncSetAttribute(gqa_fmha_kernel<192, 128, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, FmhaSmem<192, 128>::kTotal);
+    if (e0 != cudaSuccess) return e0;
+    once.mark(dev);
+  }
+  const int up = nh * 256;
+  alignas(64) CUtensorMap tq, tk, tpe;
+  cudaError_t e = make_tmap_bf16_rows(&tq, q, M, (long long)nh * 192, kFQ);
+  if (e != cudaSuccess) return e;
+  e = make_tmap_bf16_rows(&tk, kv_up, kv_len, up, kFK);
+  if (e != cudaSuccess) return e;
+  e = make_tmap_bf16_rows(&tpe, kpe, kv_len, 64, kFK);
+  if (e != cudaSuccess) return e;
+  GqaDims g{0, nh, nh, 192, 0, 0, 0.f, 0.f};
+  dim3 grid((M + kFQ - 1) / kFQ, nh);
+  KernelSpan ks(K_FMHA, s);
+  gqa_fmha_kernel<192, 128, true><<<grid, kFThreads, FmhaSmem<192, 128>::kTotal, s>>>(
+      tq, tk, tpe, tk, g, nullptr, (__nv_bfloat16*)out, M, q_start, kv_len, sm_scale * 1.4426950408889634f, 0, nh * 128, window, sinks);
   return cudaGetLastError();
 }
 

@@ -36,8 +36,18 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
       : "memory");
   return ok != 0;
 }
+// Bounded wait: a barrier that does not complete within ~2 s of SM clocks raises a sticky per-module flag and returns, so that a
+// mis-counted pipeline runs to its end (with wrong data) and releases its tensor memory instead of spinning for ever.
+static __device__ int g_mbar_timed_out = 0;
 __device__ __forceinline__ void mbar_wait(uint64_t* bar, uint32_t parity) {
+  if (mbar_try_wait(bar, parity)) return;
+  const long long t0 = clock64();
   while (!mbar_try_wait(bar, parity)) {
+    if (*reinterpret_cast<volatile int*>(&g_mbar_timed_out)) return;
+    if (clock64() - t0 > 4000000000ll) {
+      *reinterpret_cast<volatile int*>(&g_mbar_timed_out) = 1;
+      return;
+    }
   }
 }
 

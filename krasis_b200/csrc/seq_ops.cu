@@ -405,8 +405,12 @@ __global__ void __launch_bounds__(kAttnThreads) latent_window_attn_kernel(
     const float* __restrict__ q_abs, const float* __restrict__ proj, long long ldp, int H, int HG, int dn, int dr, int r,
     const void* __restrict__ ckv, const void* __restrict__ kr, int dt_cache, const int* __restrict__ positions,
     const int* __restrict__ seq_of, const int* __restrict__ pages, int max_pages, int page_size, const float* __restrict__ sinks,
-    float scale, int window, int KT, float* __restrict__ out) {
+    float scale, int window, int KT, float* __restrict__ out, const int* __restrict__ cu, int skip_from) {
   extern __shared__ __align__(16) float sm[];
+  if (cu != nullptr) {                    // sequences whose portion has skip_from tokens or more are served by another kernel
+    const int sq = seq_of[blockIdx.x];
+    if (cu[sq + 1] - cu[sq] >= skip_from) return;
+  }
   const int D = r + dr, DP = D + 1;
   long long* krow = (long long*)sm;       // [KT] cache rows of the tile's keys
   float* qs = sm + 2 * KT;                // [HG][D]
@@ -897,7 +901,7 @@ KB2SEQ_API int kb2_seq_latent_prep(float* proj, long long ldp, int T, int H, int
 KB2SEQ_API int kb2_seq_latent_window_attn(const float* q_abs, const float* proj, long long ldp, int T, int H, int dn, int dr, int r,
                                           const void* ckv, const void* kr, int dt_cache, const int* positions, const int* seq_of,
                                           const int* pages, int max_pages, int page_size, const float* sinks, float scale, int window,
-                                          float* out, void* stream) {
+                                          float* out, const int* cu, int skip_from, void* stream) {
   if (!q_abs || !proj || !ckv || !kr || !positions || !seq_of || !pages || !sinks || !out || T <= 0 || H <= 0 || r <= 0 || dr < 0 ||
       window <= 0 || bad_dt(dt_cache))
     return failf(KB2SEQ_ERR_VALUE, "latent_window_attn: bad argument");
@@ -915,7 +919,7 @@ KB2SEQ_API int kb2_seq_latent_window_attn(const float* q_abs, const float* proj,
   dim3 grid(T, (H + HG - 1) / HG);
   latent_window_attn_kernel<<<grid, kAttnThreads, smem, (cudaStream_t)stream>>>(q_abs, proj, ldp, H, HG, dn, dr, r, ckv, kr, dt_cache, positions,
                                                                                  seq_of, pages, max_pages, page_size, sinks, scale, window, KT,
-                                                                                 out);
+                                                                                 out, cu, skip_from);
   SEQ_LAUNCHED();
   return KB2SEQ_OK;
 }

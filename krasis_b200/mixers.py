@@ -94,6 +94,11 @@ class WindowLatentAttention:
         self.uk_t = d(weights["uk"].reshape(heads, dim, kv_rank).transpose(1, 2))
         self.uv = d(weights["uv"].reshape(heads, vdim, kv_rank))
         self.w_o = d(weights["o"])
+        # long prompt portions in bfloat16 with 128 + 64 query / key dims and 128 value dims run the tcgen05 attention core of the MoE
+        # prefill models (non-absorbed form: keys and values of the window are up-projected from the cached latents by one GEMM)
+        self.tc_min_portion = 128
+        self.tc_shape = dtype == torch.bfloat16 and dim == 128 and rot_dim == 64 and vdim == 128 and kv_rank % 64 == 0
+        self.w_kv_up = d(torch.cat([weights["uk"], weights["uv"]], 0)) if self.tc_shape else None
 
     def cache_dims(self):
         return self.r, self.dr
@@ -108,15 +113,28 @@ class WindowLatentAttention:
                                           self.freq.data_ptr(), self.rot_dims, self.amp, tb.positions.data_ptr(), tb.seq_of.data_ptr(),
                                           tb.pages.data_ptr(), tb.max_pages, page_size, ckv.data_ptr(), kr.data_ptr(), dtc, s))
         q = proj[:, :H * (self.dn + self.dr)].view(T, H, self.dn + self.dr)
-        q_abs = torch.empty((T, H, self.r), dtype=torch.float32, device=h.device)
-        ops.gemm_heads(q[:, :, :self.dn], self.uk_t, q_abs)
-        o_lat = torch.empty((T, H, self.r), dtype=torch.float32, device=h.device)
-        ops.check(lib.kb2_seq_latent_window_attn(q_abs.data_ptr(), proj.data_ptr(), ldp, T, H, self.dn, self.dr, self.r, ckv.data_ptr(),
-                                                 kr.data_ptr(), dtc, tb.positions.data_ptr(), tb.seq_of.data_ptr(), tb.pages.data_ptr(),
-                                                 tb.max_pages, page_size, self.sink.data_ptr(), self.scale, self.window,
-                                                 o_lat.data_ptr(), s))
         o = torch.empty((T, H, self.dv), dtype=self.dtype, device=h.device)
-        ops.gemm_heads(o_lat, self.uv, o)
+        core = _core_lib() if self.tc_shape else False
+        fast = [i for i, (_, n, _, _) in enumerate(tb.layout) if n >= self.tc_min_portion] if core else []
+        if len(fast) < tb.S:
+            q_abs = torch.empty((T, H, self.r), dtype=torch.float32, device=h.device)
+            ops.gemm_heads(q[:, :, :self.dn], self.uk_t, q_abs)
+            o_lat = torch.empty((T, H, self.r), dtype=torch.float32, device=h.device)
+            ops.check(lib.kb2_seq_latent_window_attn(q_abs.data_ptr(), proj.data_ptr(), ldp, T, H, self.dn, self.dr, self.r, ckv.data_ptr(),
+                                                     kr.data_ptr(), dtc, tb.positions.data_ptr(), tb.seq_of.data_ptr(), tb.pages.data_ptr(),
+                                                     tb.max_pages, page_size, self.sink.data_ptr(), self.scale, self.window,
+                                                     o_lat.data_ptr(), tb.cu.data_ptr() if fast else None, self.tc_min_portion, s))
+            ops.gemm_heads(o_lat, self.uv, o)
+        for i in fast:
+            from . import capi
+            row0, n, start, _ = tb.layout[i]
+            lo, rows = ops.key_rows(tb, i, self.window, page_size)
+            kv_up = lin(ckv.view(-1, self.r).index_select(0, rows), self.w_kv_up, torch.bfloat16)     # [keys, H * (128 + 128)]
+            kpe = kr.view(-1, self.dr).index_select(0, rows)
+            q_bf = proj[row0:row0 + n, :H * (self.dn + self.dr)].to(torch.bfloat16).contiguous()
+            capi.check(core.kb2_fmha_latent(q_bf.data_ptr(), kv_up.data_ptr(), kpe.data_ptr(), o[row0:row0 + n].data_ptr(), n, start - lo,
+                                            start - lo + n, H, self.scale, min(self.window, 1 << 30), self.sink.data_ptr(),
+                                            h.device.index or 0, s))
         return lin(o.view(T, H * self.dv), self.w_o, torch.float32)
 
 

@@ -22,7 +22,7 @@ SIGNATURES = {
     "kb2_seq_act_mul": (_I, [_P, _I, _P, _I, _I, _I, _P]),
     "kb2_seq_side_gate": (_I, [_P, _P, _I, _L, _P, _I, _I, _I, _P, _I, _P]),
     "kb2_seq_latent_prep": (_I, [_P, _L, _I, _I, _I, _I, _I, _P, _F, _P, _I, _F, _P, _P, _P, _I, _I, _P, _P, _I, _P]),
-    "kb2_seq_latent_window_attn": (_I, [_P, _P, _L, _I, _I, _I, _I, _I, _P, _P, _I, _P, _P, _P, _I, _I, _P, _F, _I, _P, _P]),
+    "kb2_seq_latent_window_attn": (_I, [_P, _P, _L, _I, _I, _I, _I, _I, _P, _P, _I, _P, _P, _P, _I, _I, _P, _F, _I, _P, _P, _I, _P]),
     "kb2_seq_conv_silu": (_I, [_P, _L, _I, _I, _I, _I, _P, _P, _P, _P, _P, _P, _P]),
     "kb2_seq_delta_rule": (_I, [_P, _I, _P, _L, _I, _I, _I, _I, _I, _I, _I, _I, _I, _P, _P, _P, _F, _P, _P, _P, _P, _P, _I, _P]),
 }
@@ -109,12 +109,32 @@ class StepTables:
             cu += k
         a[o_cu + S] = cu
         self.T, self.S, self.max_pages = T, S, maxp
+        # host copy of the step's layout: (first row, tokens, first position, page list) per sequence
+        self.layout, row = [], 0
+        for toks, start, _, pages in entries:
+            self.layout.append((row, len(toks), int(start), list(pages)))
+            row += len(toks)
+        self._key_rows = {}
         self.max_portion = max(len(e[0]) for e in entries)
         self.buf = host.to(device, non_blocking=True)
         self._host = host
         self.tokens, self.positions, self.seq_of = self.buf[:T], self.buf[o_pos:o_pos + T], self.buf[o_seq:o_seq + T]
         self.cu, self.slots, self.pages = self.buf[o_cu:o_cu + S + 1], self.buf[o_slot:o_slot + S], self.buf[o_pg:]
         self.h2d_bytes = n * 4
+
+
+def key_rows(tb: StepTables, s: int, window: int, page_size: int):
+    """Cache rows of the keys sequence s needs in this step under a sliding window: (first key position, int64 rows on the device),
+    computed once per step and window size."""
+    key = (s, window, page_size)
+    if key not in tb._key_rows:
+        import numpy as np
+        _, n, start, pages = tb.layout[s]
+        lo = max(0, start - window + 1)
+        j = np.arange(lo, start + n, dtype=np.int64)
+        rows = np.asarray(pages, dtype=np.int64)[j // page_size] * page_size + j % page_size
+        tb._key_rows[key] = (lo, torch.from_numpy(rows).to(tb.buf.device, non_blocking=True))
+    return tb._key_rows[key]
 
 
 def embed(table: torch.Tensor, tokens: torch.Tensor, scale: float) -> torch.Tensor:

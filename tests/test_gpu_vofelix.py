@@ -222,6 +222,38 @@ def test_latent_attention_bfloat16_cache_and_decode_grids(seq):
         close(b, want, tol, f"{dtype} portion + decoding")
 
 
+def test_tensor_core_prefill_of_latent_attention(seq):
+    """bfloat16, 128 + 64 query / key dims, 128 value dims: portions of 128 tokens or more run the tcgen05 attention core on keys and
+    values up-projected from the cached latents.  Against the oracle, and against the plain kernel on the same bf16 cache, with peaked
+    scores and heavy sinks, windows that end inside, at and across KV tiles, portions that start in the middle of a window."""
+    from krasis_b200.build import build as build_core
+    build_core()
+    for window, sink_shift, scale in ((100, 2.0, 0.25), (64, 0.0, 0.15), (333, 3.0, 0.3), (None, 1.0, 0.2)):
+        raw = _one_layer("latent_attention", latent_cfg(heads=2, dim=128, rot_dim=64, vdim=128, kv_rank=64, window=window, scale=scale), width=64)
+
+        def tweak(w):
+            for k in w:
+                if k.endswith("mix.sink"):
+                    w[k] = w[k] + sink_shift
+        model, w = build(raw, dtype=torch.bfloat16, seed=31, tweak=tweak)
+        mixer = model.layers[0]["mixer"]
+        assert mixer.tc_shape
+        tk = toks(700, raw["vocab"], 16)
+        want = O.forward(raw, w, tk)
+        if window:                                  # the window's edge must move the logits by far more than the tolerances below
+            wide = {**raw, "layers": [{**raw["layers"][0], "mixer": {**raw["layers"][0]["mixer"], "mask": {"size": window + 1}}}]}
+            assert np.abs(O.forward(wide, w, tk) - want).max() > 0.15 * np.abs(want).max()
+        fast_whole = run_portions(model, tk, [700], s=sched(model, 1024))
+        fast_parts = run_portions(model, tk, [130, 257, 128, 150], s=sched(model, 1024))          # then 35 single tokens through the plain kernel
+        mixer.tc_min_portion = 1 << 30
+        plain = run_portions(model, tk, [700], s=sched(model, 1024))
+        mixer.tc_min_portion = 128
+        close(plain, want, 5e-2, f"window {window}: plain kernel against the oracle")
+        close(fast_whole, want, 5e-2, f"window {window}: tensor-core prefill against the oracle")
+        close(fast_whole, plain, 3e-2, f"window {window}: tensor-core prefill against the plain kernel")
+        close(fast_parts, plain, 3e-2, f"window {window}: tensor-core portions against the plain kernel")
+
+
 def test_mlp_and_side_alone(seq):
     raw = _one_layer("delta", delta_cfg(), ff=72, side=10)
     model, w = build(raw, seed=13)
