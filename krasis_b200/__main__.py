@@ -42,7 +42,7 @@ def main(argv=None) -> int:
         print(f"{type(model).__name__} has no step interface for generation", file=sys.stderr)
         return 3
     prompts = [[int(t) for t in p.split(",") if t.strip()] for p in a.prompt_ids]
-    sched = Scheduler(model, max_tokens=a.max_tokens, max_requests=a.max_requests)
+    sched = Scheduler(model, max_tokens=a.max_tokens, max_requests=a.max_requests, cuda_graphs=True)
     outs = sched.generate(prompts, a.max_new_tokens, SamplingParams(a.temperature, a.top_k, a.top_p, a.seed), step_tokens=a.step_tokens,
                           eos=a.eos)
     for p, o in zip(prompts, outs):

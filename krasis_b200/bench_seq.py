@@ -73,12 +73,13 @@ def run(args, peaks):
 
     # ---- decode: 4 live requests with `ctx` tokens each, one token per request per step
     ctx = 2048
-    s = Scheduler(model, max_tokens=4 * (ctx + 256), max_requests=4)
+    s = Scheduler(model, max_tokens=4 * (ctx + 256), max_requests=4, cuda_graphs=not getattr(args, 'no_graph', False))
     for r in range(4):
         s.step([(r, prompt[:ctx], [])])
     nxt = [[1], [2], [3], [4]]
     ms_d = _time(lambda: s.step([(r, nxt[r], [0]) for r in range(4)]), args.warmup, 16)
-    out["decode"] = {"live_requests": 4, "context": ctx, "tokens_per_s": round(4 / ms_d * 1e3, 1), "ms_per_step": round(ms_d, 3)}
+    out["decode"] = {"live_requests": 4, "context": ctx, "tokens_per_s": round(4 / ms_d * 1e3, 1), "ms_per_step": round(ms_d, 3),
+                     "cuda_graph": bool(s.cuda_graphs and any(v not in (None, False) for v in s._graphs.values()))}
     out["gpu_launches"] = ops.total_launches() - launches0
 
     # ---- end to end through the generation entry point: pinned host tables in, sampled ids out every step

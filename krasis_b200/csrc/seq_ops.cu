@@ -201,7 +201,9 @@ template <> __device__ __forceinline__ void load8<float>(const float* p, float* 
 }
 template <> __device__ __forceinline__ void load8<bf16>(const bf16* p, float* f) { unpack8(*reinterpret_cast<const uint4*>(p), f); }
 
-template <typename TA, typename TC, int MR>
+// A warp owns CPW neighbouring output columns: the rows of A it loads (L1 hits after the first warp) serve CPW weight rows, and CPW
+// 16-byte weight loads per lane are in flight at once.
+template <typename TA, typename TC, int MR, int CPW>
 __global__ void __launch_bounds__(256) gemv_nt_vec_kernel(const TA* __restrict__ A, long long lda, const bf16* __restrict__ B, long long ldb,
                                                           TC* __restrict__ C, long long ldc, int M, int N, int K, long long sA,
                                                           long long sB, long long sC) {
@@ -209,28 +211,38 @@ __global__ void __launch_bounds__(256) gemv_nt_vec_kernel(const TA* __restrict__
   B += (long long)blockIdx.z * sB;
   C += (long long)blockIdx.z * sC;
   const int lane = threadIdx.x & 31;
-  const int n = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
-  if (n >= N) return;
-  float acc[MR];
+  const int n0 = (blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5)) * CPW;
+  if (n0 >= N) return;
+  float acc[MR][CPW];
 #pragma unroll
-  for (int m = 0; m < MR; ++m) acc[m] = 0.f;
-  const bf16* b = B + (long long)n * ldb;
+  for (int m = 0; m < MR; ++m)
+#pragma unroll
+    for (int c = 0; c < CPW; ++c) acc[m][c] = 0.f;
   for (int k = lane * 8; k < K; k += 256) {
-    float w[8], a[8];
-    unpack8(*reinterpret_cast<const uint4*>(b + k), w);
+    uint4 wv[CPW];
+#pragma unroll
+    for (int c = 0; c < CPW; ++c) wv[c] = (n0 + c < N) ? *reinterpret_cast<const uint4*>(B + (long long)(n0 + c) * ldb + k) : make_uint4(0, 0, 0, 0);
 #pragma unroll
     for (int m = 0; m < MR; ++m)
       if (m < M) {
+        float a[8];
         load8<TA>(A + (long long)m * lda + k, a);
 #pragma unroll
-        for (int i = 0; i < 8; ++i) acc[m] = fmaf(a[i], w[i], acc[m]);
+        for (int c = 0; c < CPW; ++c) {
+          float w[8];
+          unpack8(wv[c], w);
+#pragma unroll
+          for (int i = 0; i < 8; ++i) acc[m][c] = fmaf(a[i], w[i], acc[m][c]);
+        }
       }
   }
 #pragma unroll
-  for (int m = 0; m < MR; ++m) {
-    const float v = warp_sum(acc[m]);
-    if (lane == 0 && m < M) stf(C, (long long)m * ldc + n, v);
-  }
+  for (int m = 0; m < MR; ++m)
+#pragma unroll
+    for (int c = 0; c < CPW; ++c) {
+      const float v = warp_sum(acc[m][c]);
+      if (lane == 0 && m < M && n0 + c < N) stf(C, (long long)m * ldc + n0 + c, v);
+    }
 }
 
 template <typename TA, typename TC>
@@ -238,8 +250,18 @@ static bool launch_gemv_vec(const void* A, long long lda, const void* B, long lo
                             int batch, long long sA, long long sB, long long sC, cudaStream_t s) {
   const bool a16 = sizeof(TA) == 2;
   if (K % 8 || ldb % 8 || sB % 8 || ((uintptr_t)B & 15) || ((uintptr_t)A & 15) || lda % (a16 ? 8 : 4) || sA % (a16 ? 8 : 4)) return false;
-  dim3 grid((N + 7) / 8, 1, batch);
-  gemv_nt_vec_kernel<TA, TC, 8><<<grid, 256, 0, s>>>((const TA*)A, lda, (const bf16*)B, ldb, (TC*)C, ldc, M, N, K, sA, sB, sC);
+  // columns per warp: 4 where that still leaves two blocks per SM, else fewer
+  const long long warps = (long long)N * batch;
+  if (warps >= 4 * 8 * 296) {
+    dim3 grid((N + 31) / 32, 1, batch);
+    gemv_nt_vec_kernel<TA, TC, 8, 4><<<grid, 256, 0, s>>>((const TA*)A, lda, (const bf16*)B, ldb, (TC*)C, ldc, M, N, K, sA, sB, sC);
+  } else if (warps >= 2 * 8 * 296) {
+    dim3 grid((N + 15) / 16, 1, batch);
+    gemv_nt_vec_kernel<TA, TC, 8, 2><<<grid, 256, 0, s>>>((const TA*)A, lda, (const bf16*)B, ldb, (TC*)C, ldc, M, N, K, sA, sB, sC);
+  } else {
+    dim3 grid((N + 7) / 8, 1, batch);
+    gemv_nt_vec_kernel<TA, TC, 8, 1><<<grid, 256, 0, s>>>((const TA*)A, lda, (const bf16*)B, ldb, (TC*)C, ldc, M, N, K, sA, sB, sC);
+  }
   return true;
 }
 

@@ -202,5 +202,7 @@ class TokenSideInput:
         self.table, self.col0, self.dim, self.dtype = table, col0, dim, dtype
 
     def forward(self, x: torch.Tensor, tb: ops.StepTables) -> torch.Tensor:
-        g = lin(x, self.w_gate, torch.float32)                                     # x: the fp32 residual stream itself
+        # x is the fp32 residual stream itself; a long bfloat16 step rounds it once so that the projection runs on the tensor cores
+        a = x.to(torch.bfloat16) if (self.dtype == torch.bfloat16 and x.shape[0] >= 256 and _core_lib()) else x
+        g = lin(a, self.w_gate, torch.float32)
         return lin(ops.side_gate(g, self.table, tb.tokens, self.col0, self.dtype), self.w_proj, torch.float32)

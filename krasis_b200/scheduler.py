@@ -32,8 +32,13 @@ class Request:
 
 
 class Scheduler:
-    def __init__(self, model, max_tokens: int, max_requests: int = 4):
+    def __init__(self, model, max_tokens: int, max_requests: int = 4, cuda_graphs: bool = False):
+        """cuda_graphs: steps in which every entry brings one token (decoding) are captured once per (entries, page-list width) and
+        replayed — same kernels, the Python launch path off the critical path.  The tables of a replayed step are copied into the
+        fixed device buffer the graph reads; a capture that fails leaves the eager path in charge."""
         self.model, self.max_requests = model, max_requests
+        self.cuda_graphs = bool(cuda_graphs) and torch.cuda.is_available()
+        self._graphs = {}
         self.kv_cache, self.state_pool = model.make_caches(max_tokens, max_requests)
         self.live: Dict[object, Request] = {}
         self.steps_run = 0
@@ -72,14 +77,66 @@ class Scheduler:
             packed.append((tokens, req.kv.seq_len, req.slot, req.kv.pages))
             rows += [cu + int(w) for w in want]
             cu += len(tokens)
-        tb = ops.StepTables(packed, self.model.device)
-        self.h2d_bytes += tb.h2d_bytes
-        want_rows = torch.tensor(rows, dtype=torch.int64, device=self.model.device) if rows else None
-        logits = self.model.forward_step(tb, want_rows)
+        ran, logits = False, None
+        if self.cuda_graphs and cu == len(entries):
+            ran, logits = self._decode_step_graphed(packed, rows)
+        if not ran:
+            tb = ops.StepTables(packed, self.model.device)
+            self.h2d_bytes += tb.h2d_bytes
+            want_rows = torch.tensor(rows, dtype=torch.int64, device=self.model.device) if rows else None
+            logits = self.model.forward_step(tb, want_rows)
         for rid, tokens, _ in entries:
             self.live[rid].kv.advance(len(tokens))
         self.steps_run += 1
         return logits
+
+    def _decode_step_graphed(self, packed, rows):
+        """One decoded token per entry, replayed from a CUDA graph.  Returns (ran, logits); ran is False where the eager path has to run."""
+        dev, S = self.model.device, len(packed)
+        maxp = (max(1, max(len(e[3]) for e in packed)) + 7) // 8 * 8
+        key = (S, maxp)
+        ent = self._graphs.get(key)
+        if ent is False:
+            return False, None
+        if ent is None:
+            try:
+                n = 3 * S + (S + 1) + S + S * maxp
+                buf = torch.zeros(n, dtype=torch.int32, device=dev)
+                all_rows = torch.arange(S, dtype=torch.int64, device=dev)
+                tb = ops.StepTables(packed, dev, pad_pages_to=8, device_buf=buf)
+                # snapshot of every recurrent state: warm-up and capture run the step for real, the replay must start from here
+                saved = [t.clone() for t in self.state_pool.tensors]
+                side = torch.cuda.Stream(dev)
+                side.wait_stream(torch.cuda.current_stream(dev))
+                with torch.cuda.stream(side):
+                    self.model.forward_step(tb, all_rows)
+                torch.cuda.current_stream(dev).wait_stream(side)
+                torch.cuda.synchronize(dev)
+                graph = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(graph):
+                    out = self.model.forward_step(tb, all_rows)
+                for t, sv in zip(self.state_pool.tensors, saved):
+                    t.copy_(sv)
+                ent = (graph, buf, out, all_rows)          # everything the captured launches read stays alive with the graph
+                self._graphs[key] = ent
+            except Exception as exc:            # noqa: BLE001 — never a wrong result: fall back to eager launches
+                import warnings
+                warnings.warn(f"CUDA graph capture of a decode step failed ({exc}); using eager launches")
+                self._graphs[key] = False
+                try:
+                    torch.cuda.synchronize(dev)
+                except Exception:               # noqa: BLE001
+                    pass
+                return False, None
+        graph, buf, out, _ = ent
+        tb = ops.StepTables(packed, dev, pad_pages_to=8, device_buf=buf)
+        self.h2d_bytes += tb.h2d_bytes
+        graph.replay()
+        if not rows:
+            return True, None
+        if rows == list(range(S)):
+            return True, out.clone()            # the graph's own output buffer is overwritten by the next replay
+        return True, out.index_select(0, torch.tensor(rows, dtype=torch.int64, device=dev))
 
     # ------------------------------------------------------------------------------------------- generation
     def generate(self, prompts: Sequence[Sequence[int]], max_new_tokens: int, sampling: Optional[SamplingParams] = None,

@@ -87,11 +87,14 @@ class StepTables:
 
     entries: [(tokens, start_position, state_slot, page_list)] in batch order."""
 
-    def __init__(self, entries, device):
+    def __init__(self, entries, device, pad_pages_to: int = 1, device_buf=None):
+        """pad_pages_to rounds the page-list width up (fewer distinct shapes); device_buf, if given, is a device int32 buffer of the
+        right size that receives the tables (a captured CUDA graph reads its tables from a fixed buffer)."""
         import numpy as np
         S = len(entries)
         T = sum(len(e[0]) for e in entries)
         maxp = max(1, max(len(e[3]) for e in entries))
+        maxp = (maxp + pad_pages_to - 1) // pad_pages_to * pad_pages_to
         n = 3 * T + (S + 1) + S + S * maxp
         host = torch.empty(n, dtype=torch.int32, pin_memory=torch.cuda.is_available())
         a = host.numpy()
@@ -116,7 +119,14 @@ class StepTables:
             row += len(toks)
         self._key_rows = {}
         self.max_portion = max(len(e[0]) for e in entries)
-        self.buf = host.to(device, non_blocking=True)
+        if device_buf is not None:
+            if device_buf.numel() != n:
+                raise ValueError("device_buf does not fit this step's tables")
+            device_buf.copy_(host, non_blocking=True)
+            self.buf = device_buf
+        else:
+            self.buf = host.to(device, non_blocking=True)
+        self.numel = n
         self._host = host
         self.tokens, self.positions, self.seq_of = self.buf[:T], self.buf[o_pos:o_pos + T], self.buf[o_seq:o_seq + T]
         self.cu, self.slots, self.pages = self.buf[o_cu:o_cu + S + 1], self.buf[o_slot:o_slot + S], self.buf[o_pg:]

@@ -443,6 +443,34 @@ def test_greedy_generation_through_the_entry_point(seq):
     assert checked >= 40
 
 
+def test_decode_steps_replayed_from_cuda_graphs_equal_eager_steps(seq):
+    """Decode steps captured per (live requests, page-list width) and replayed: bit-identical logits, over page borders (new
+    page-list widths re-capture), with a request joining and one leaving, and a prompt portion in between (eager)."""
+    from krasis_b200.scheduler import Scheduler
+    raw = model_cfg(default_layers())
+    model, w = build(raw, seed=17, page_size=4)
+    a, b, c = toks(90, 50, 1), toks(70, 50, 2), toks(40, 50, 3)
+    outs = []
+    for graphs in (False, True):
+        s = Scheduler(model, max_tokens=512, max_requests=3, cuda_graphs=graphs)
+        got = [s.step([("a", a[:20], [19]), ("b", b[:5], [4])])]
+        for i in range(40):
+            got.append(s.step([("a", [a[20 + i]], [0]), ("b", [b[5 + i]], [0])]))
+        got.append(s.step([("c", c[:30], [29]), ("a", [a[60]], [0])]))
+        for i in range(10):
+            got.append(s.step([("a", [a[61 + i]], [0]), ("b", [b[45 + i]], []), ("c", [c[30 + i]], [0])]))
+        s.finish("b")
+        for i in range(10):
+            got.append(s.step([("c", [c[30 + i]], [0]), ("a", [a[71 + i]], [0])]))
+        outs.append([g.clone() for g in got])
+        if graphs:
+            assert sum(1 for v in s._graphs.values() if v) >= 3
+    for x, y in zip(*outs):
+        assert torch.equal(x, y)
+    want = O.forward(raw, w, a[:81])
+    close(outs[1][-1][1].cpu().numpy(), want[80], 5e-5, "last decoded token of request a")
+
+
 def test_registry_loads_a_checkpoint_directory(seq, tmp_path):
     """config.json + model.safetensors on disk -> registry -> model -> same logits as the oracle."""
     import json
