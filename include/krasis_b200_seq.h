@@ -58,11 +58,14 @@ KB2SEQ_API int kb2_seq_latent_prep(float* proj, long long ldp, int T, int H, int
                                    const int* pages, int max_pages, int page_size, void* ckv, void* kr, int dt_cache, void* stream);
 
 /* out[t, h, :r] = sum_j softmax_j(...) latent_j over the keys with 0 <= pos - j < window; the denominator also holds exp(sinks[h]).
- * With cu != NULL the tokens of sequences whose portion has skip_from tokens or more are left out (another kernel serves them). */
+ * With cu != NULL the tokens of sequences whose portion has skip_from tokens or more are left out (another kernel serves them).
+ * nsplit > 1 cuts every token's key range into nsplit pieces that run as separate blocks (steps of few tokens: decoding) and are merged
+ * by a second kernel; part_acc [T][nsplit][H][r] and part_ml [T][nsplit][H][2] (fp32) hold the pieces. */
 KB2SEQ_API int kb2_seq_latent_window_attn(const float* q_abs, const float* proj, long long ldp, int T, int H, int dn, int dr, int r,
                                           const void* ckv, const void* kr, int dt_cache, const int* positions, const int* seq_of,
                                           const int* pages, int max_pages, int page_size, const float* sinks, float scale, int window,
-                                          float* out, const int* cu, int skip_from, void* stream);
+                                          float* out, const int* cu, int skip_from, int nsplit, float* part_acc, float* part_ml,
+                                          void* stream);
 
 /* out[t, c] = silu(causal conv over time of proj[:, c], K taps) for c < C; tail [slots][C][K - 1] is read, then advanced */
 KB2SEQ_API int kb2_seq_conv_silu(const float* proj, long long ldp, int T, int S, int C, int K, const float* taps, float* tail,

@@ -427,7 +427,8 @@ __global__ void __launch_bounds__(kAttnThreads) latent_window_attn_kernel(
     const float* __restrict__ q_abs, const float* __restrict__ proj, long long ldp, int H, int HG, int dn, int dr, int r,
     const void* __restrict__ ckv, const void* __restrict__ kr, int dt_cache, const int* __restrict__ positions,
     const int* __restrict__ seq_of, const int* __restrict__ pages, int max_pages, int page_size, const float* __restrict__ sinks,
-    float scale, int window, int KT, float* __restrict__ out, const int* __restrict__ cu, int skip_from) {
+    float scale, int window, int KT, float* __restrict__ out, const int* __restrict__ cu, int skip_from, int nsplit,
+    float* __restrict__ part_acc, float* __restrict__ part_ml) {
   extern __shared__ __align__(16) float sm[];
   if (cu != nullptr) {                    // sequences whose portion has skip_from tokens or more are served by another kernel
     const int sq = seq_of[blockIdx.x];
@@ -451,16 +452,25 @@ __global__ void __launch_bounds__(kAttnThreads) latent_window_attn_kernel(
     const int hh = i / D, d = i - hh * D;
     qs[i] = d < r ? q_abs[(t * H + h0 + hh) * r + d] : proj[t * ldp + (long long)(h0 + hh) * (dn + dr) + dn + (d - r)];
   }
+  // nsplit > 1: block z takes the z-th piece of the token's key range and leaves an unnormalised partial result (running max, sum,
+  // weighted latents) for latent_attn_combine_kernel; the sink belongs to piece 0
+  const int z = blockIdx.z;
   if (tid < nh) {
-    m_run[tid] = sinks[h0 + tid];
-    l_run[tid] = 1.f;
+    m_run[tid] = z == 0 ? sinks[h0 + tid] : -INFINITY;
+    l_run[tid] = z == 0 ? 1.f : 0.f;
   }
   float acc[kAttnAcc];
 #pragma unroll
   for (int a = 0; a < kAttnAcc; ++a) acc[a] = 0.f;
   const int j_lo = max(0, pos - window + 1);
-  for (int j0 = j_lo; j0 <= pos; j0 += KT) {
-    const int nk = min(KT, pos - j0 + 1);
+  int j_begin = j_lo, j_end = pos;
+  if (nsplit > 1) {
+    const int piece = (((pos - j_lo + 1) + nsplit - 1) / nsplit + KT - 1) / KT * KT;
+    j_begin = j_lo + z * piece;
+    j_end = min(pos, j_begin + piece - 1);
+  }
+  for (int j0 = j_begin; j0 <= j_end; j0 += KT) {
+    const int nk = min(KT, j_end - j0 + 1);
     __syncthreads();
     if (tid < nk) {
       const int j = j0 + tid;
@@ -523,7 +533,7 @@ __global__ void __launch_bounds__(kAttnThreads) latent_window_attn_kernel(
         lsum += warp_sum(p);
       }
       if (lane == 0) {
-        const float al = expf(m_old - m_new);
+        const float al = m_old == -INFINITY ? 0.f : expf(m_old - m_new);
         alpha[hh] = al;
         l_run[hh] = l_run[hh] * al + lsum;
         m_run[hh] = m_new;
@@ -548,8 +558,43 @@ __global__ void __launch_bounds__(kAttnThreads) latent_window_attn_kernel(
     const int i = tid + a * kAttnThreads;
     if (i < nh * r) {
       const int hh = i / r, d = i - hh * r;
-      out[(t * H + h0 + hh) * r + d] = acc[a] / l_run[hh];
+      if (nsplit > 1) part_acc[((t * nsplit + z) * H + h0 + hh) * r + d] = acc[a];
+      else out[(t * H + h0 + hh) * r + d] = acc[a] / l_run[hh];
     }
+  }
+  if (nsplit > 1 && tid < nh) {
+    part_ml[((t * nsplit + z) * H + h0 + tid) * 2] = m_run[tid];
+    part_ml[((t * nsplit + z) * H + h0 + tid) * 2 + 1] = l_run[tid];
+  }
+}
+
+// out[t, h, :] = sum_z w_z acc_z / sum_z w_z l_z with w_z = exp(m_z - max_z m_z); pieces without keys have l_z = 0
+__global__ void __launch_bounds__(128) latent_attn_combine_kernel(const float* __restrict__ part_acc, const float* __restrict__ part_ml,
+                                                                  int H, int r, int nsplit, float* __restrict__ out,
+                                                                  const int* __restrict__ seq_of, const int* __restrict__ cu, int skip_from) {
+  const long long t = blockIdx.x;
+  const int h = blockIdx.y;
+  if (cu != nullptr) {
+    const int sq = seq_of[t];
+    if (cu[sq + 1] - cu[sq] >= skip_from) return;
+  }
+  float M = -INFINITY;
+  for (int zz = 0; zz < nsplit; ++zz) {
+    const float* ml = part_ml + ((t * nsplit + zz) * H + h) * 2;
+    if (ml[1] > 0.f) M = fmaxf(M, ml[0]);
+  }
+  float L = 0.f;
+  for (int zz = 0; zz < nsplit; ++zz) {
+    const float* ml = part_ml + ((t * nsplit + zz) * H + h) * 2;
+    if (ml[1] > 0.f) L += ml[1] * expf(ml[0] - M);
+  }
+  for (int d = threadIdx.x; d < r; d += blockDim.x) {
+    float v = 0.f;
+    for (int zz = 0; zz < nsplit; ++zz) {
+      const float* ml = part_ml + ((t * nsplit + zz) * H + h) * 2;
+      if (ml[1] > 0.f) v = fmaf(part_acc[((t * nsplit + zz) * H + h) * r + d], expf(ml[0] - M), v);
+    }
+    out[(t * H + h) * r + d] = v / L;
   }
 }
 
@@ -923,7 +968,8 @@ KB2SEQ_API int kb2_seq_latent_prep(float* proj, long long ldp, int T, int H, int
 KB2SEQ_API int kb2_seq_latent_window_attn(const float* q_abs, const float* proj, long long ldp, int T, int H, int dn, int dr, int r,
                                           const void* ckv, const void* kr, int dt_cache, const int* positions, const int* seq_of,
                                           const int* pages, int max_pages, int page_size, const float* sinks, float scale, int window,
-                                          float* out, const int* cu, int skip_from, void* stream) {
+                                          float* out, const int* cu, int skip_from, int nsplit, float* part_acc, float* part_ml,
+                                          void* stream) {
   if (!q_abs || !proj || !ckv || !kr || !positions || !seq_of || !pages || !sinks || !out || T <= 0 || H <= 0 || r <= 0 || dr < 0 ||
       window <= 0 || bad_dt(dt_cache))
     return failf(KB2SEQ_ERR_VALUE, "latent_window_attn: bad argument");
@@ -934,15 +980,19 @@ KB2SEQ_API int kb2_seq_latent_window_attn(const float* q_abs, const float* proj,
   const int KT = 32;
   auto smem_of = [&](int hg, int kt) { return (size_t)(hg * D + kt * (D + 1) + hg * kt + 8 * kt + 3 * hg) * 4 + (size_t)kt * 8; };
   while (HG > 1 && smem_of(HG, KT) > 200 * 1024) HG >>= 1;
-  while (HG > 1 && (long long)T * ((H + HG - 1) / HG) < 296) HG >>= 1;     // few tokens (decode): more blocks, finer pieces
+  if (nsplit < 1 || nsplit > 1024 || (nsplit > 1 && (!part_acc || !part_ml))) return failf(KB2SEQ_ERR_VALUE, "latent_window_attn: bad key split");
   const size_t smem = smem_of(HG, KT);
   if (smem > 200 * 1024) return failf(KB2SEQ_ERR_VALUE, "latent_window_attn: latent + rotated size %d too large", D);
   if (smem > 48 * 1024) SEQ_CUDA(cudaFuncSetAttribute(latent_window_attn_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-  dim3 grid(T, (H + HG - 1) / HG);
+  dim3 grid(T, (H + HG - 1) / HG, nsplit);
   latent_window_attn_kernel<<<grid, kAttnThreads, smem, (cudaStream_t)stream>>>(q_abs, proj, ldp, H, HG, dn, dr, r, ckv, kr, dt_cache, positions,
                                                                                  seq_of, pages, max_pages, page_size, sinks, scale, window, KT,
-                                                                                 out, cu, skip_from);
+                                                                                 out, cu, skip_from, nsplit, part_acc, part_ml);
   SEQ_LAUNCHED();
+  if (nsplit > 1) {
+    latent_attn_combine_kernel<<<dim3(T, H), 128, 0, (cudaStream_t)stream>>>(part_acc, part_ml, H, r, nsplit, out, seq_of, cu, skip_from);
+    SEQ_LAUNCHED();
+  }
   return KB2SEQ_OK;
 }
 

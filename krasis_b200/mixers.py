@@ -120,10 +120,18 @@ class WindowLatentAttention:
             q_abs = torch.empty((T, H, self.r), dtype=torch.float32, device=h.device)
             ops.gemm_heads(q[:, :, :self.dn], self.uk_t, q_abs)
             o_lat = torch.empty((T, H, self.r), dtype=torch.float32, device=h.device)
+            # a step of few tokens (decoding) cuts each token's keys into pieces so that the whole GPU works on them
+            blocks = T * ((H + 7) // 8)
+            max_keys = max(min(self.window, start + n) for _, n, start, _ in tb.layout)
+            nsplit = max(1, min(296 // max(blocks, 1), (max_keys + 31) // 32, 64))
+            part_acc = torch.empty((T, nsplit, H, self.r), dtype=torch.float32, device=h.device) if nsplit > 1 else None
+            part_ml = torch.empty((T, nsplit, H, 2), dtype=torch.float32, device=h.device) if nsplit > 1 else None
             ops.check(lib.kb2_seq_latent_window_attn(q_abs.data_ptr(), proj.data_ptr(), ldp, T, H, self.dn, self.dr, self.r, ckv.data_ptr(),
                                                      kr.data_ptr(), dtc, tb.positions.data_ptr(), tb.seq_of.data_ptr(), tb.pages.data_ptr(),
                                                      tb.max_pages, page_size, self.sink.data_ptr(), self.scale, self.window,
-                                                     o_lat.data_ptr(), tb.cu.data_ptr() if fast else None, self.tc_min_portion, s))
+                                                     o_lat.data_ptr(), tb.cu.data_ptr() if fast else None, self.tc_min_portion, nsplit,
+                                                     part_acc.data_ptr() if nsplit > 1 else None,
+                                                     part_ml.data_ptr() if nsplit > 1 else None, s))
             ops.gemm_heads(o_lat, self.uv, o)
         for i in fast:
             from . import capi

@@ -22,7 +22,7 @@ SIGNATURES = {
     "kb2_seq_act_mul": (_I, [_P, _I, _P, _I, _I, _I, _P]),
     "kb2_seq_side_gate": (_I, [_P, _P, _I, _L, _P, _I, _I, _I, _P, _I, _P]),
     "kb2_seq_latent_prep": (_I, [_P, _L, _I, _I, _I, _I, _I, _P, _F, _P, _I, _F, _P, _P, _P, _I, _I, _P, _P, _I, _P]),
-    "kb2_seq_latent_window_attn": (_I, [_P, _P, _L, _I, _I, _I, _I, _I, _P, _P, _I, _P, _P, _P, _I, _I, _P, _F, _I, _P, _P, _I, _P]),
+    "kb2_seq_latent_window_attn": (_I, [_P, _P, _L, _I, _I, _I, _I, _I, _P, _P, _I, _P, _P, _P, _I, _I, _P, _F, _I, _P, _P, _I, _I, _P, _P, _P]),
     "kb2_seq_conv_silu": (_I, [_P, _L, _I, _I, _I, _I, _P, _P, _P, _P, _P, _P, _P]),
     "kb2_seq_delta_rule": (_I, [_P, _I, _P, _L, _I, _I, _I, _I, _I, _I, _I, _I, _I, _P, _P, _P, _F, _P, _P, _P, _P, _P, _I, _P]),
 }
