@@ -65,6 +65,16 @@ __device__ __forceinline__ void st_dt(void* p, int dt, long long i, float v) {
   if (dt) ((bf16*)p)[i] = __float2bfloat16_rn(v); else ((float*)p)[i] = v;
 }
 
+// eight bf16 values of one 16-byte load
+__device__ __forceinline__ void unpack8(const uint4& v, float* f) {
+  const __nv_bfloat162* p = reinterpret_cast<const __nv_bfloat162*>(&v);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const float2 t = __bfloat1622float2(p[i]);
+    f[2 * i] = t.x;
+    f[2 * i + 1] = t.y;
+  }
+}
 __device__ __forceinline__ float gelu_tanh(float z) {
   return 0.5f * z * (1.f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z)));
 }
@@ -184,16 +194,6 @@ __global__ void __launch_bounds__(256) gemv_nt_kernel(const TA* __restrict__ A, 
   }
 }
 
-// bf16 weights, K a multiple of 8, 16-byte aligned rows: a lane reads 8 weights per load
-__device__ __forceinline__ void unpack8(const uint4& v, float* f) {
-  const __nv_bfloat162* p = reinterpret_cast<const __nv_bfloat162*>(&v);
-#pragma unroll
-  for (int i = 0; i < 4; ++i) {
-    const float2 t = __bfloat1622float2(p[i]);
-    f[2 * i] = t.x;
-    f[2 * i + 1] = t.y;
-  }
-}
 template <typename TA> __device__ __forceinline__ void load8(const TA* p, float* f);
 template <> __device__ __forceinline__ void load8<float>(const float* p, float* f) {
   const float4 a = *reinterpret_cast<const float4*>(p), b = *reinterpret_cast<const float4*>(p + 4);
@@ -350,12 +350,25 @@ __global__ void __launch_bounds__(256) residual_norm_kernel(float* __restrict__ 
 
 // ------------------------------------------------------------------------------------------------ elementwise
 __global__ void act_mul_kernel(const void* __restrict__ in, int dt_in, void* __restrict__ out, int dt_out, long long T, int F) {
-  const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
-  if (i >= T * F) return;
-  const long long t = i / F;
-  const int f = (int)(i - t * F);
+  const long long t = blockIdx.y;
+  const int f = blockIdx.x * blockDim.x + threadIdx.x;
+  if (f >= F) return;
   const float a = ld_dt(in, dt_in, t * 2 * F + f), b = ld_dt(in, dt_in, t * 2 * F + F + f);
-  st_dt(out, dt_out, i, gelu_tanh(a) * b);
+  st_dt(out, dt_out, t * F + f, gelu_tanh(a) * b);
+}
+// bf16 in and out, F a multiple of 8: 16-byte accesses
+__global__ void act_mul_bf16x8_kernel(const bf16* __restrict__ in, bf16* __restrict__ out, int F) {
+  const long long t = blockIdx.y;
+  const int f = (blockIdx.x * blockDim.x + threadIdx.x) * 8;
+  if (f >= F) return;
+  float a[8], b[8];
+  unpack8(*reinterpret_cast<const uint4*>(in + t * 2 * F + f), a);
+  unpack8(*reinterpret_cast<const uint4*>(in + t * 2 * F + F + f), b);
+  uint4 o;
+  __nv_bfloat162* po = reinterpret_cast<__nv_bfloat162*>(&o);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) po[i] = __floats2bfloat162_rn(gelu_tanh(a[2 * i]) * b[2 * i], gelu_tanh(a[2 * i + 1]) * b[2 * i + 1]);
+  *reinterpret_cast<uint4*>(out + t * F + f) = o;
 }
 
 __global__ void side_gate_kernel(const float* __restrict__ g, const void* __restrict__ table, int dt_table, long long table_ld,
@@ -604,10 +617,10 @@ __global__ void __launch_bounds__(128) latent_attn_combine_kernel(const float* _
 __global__ void conv_silu_kernel(const float* __restrict__ proj, long long ldp, int C, int K, const float* __restrict__ taps,
                                  const float* __restrict__ tail, const int* __restrict__ seq_of, const int* __restrict__ cu,
                                  const int* __restrict__ slots, long long T, float* __restrict__ out) {
-  const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
-  if (idx >= T * C) return;
-  const long long t = idx / C;
-  const int c = (int)(idx - t * C);
+  const long long t = blockIdx.y;
+  const int c = blockIdx.x * blockDim.x + threadIdx.x;
+  if (c >= C) return;
+  const long long idx = t * C + c;
   const int s = seq_of[t];
   const int i = (int)(t - cu[s]);
   const float* tl = tail + ((long long)slots[s] * C + c) * (K - 1);
@@ -936,8 +949,11 @@ KB2SEQ_API int kb2_seq_residual_norm(float* x, const float* y, int y_mode, const
 
 KB2SEQ_API int kb2_seq_act_mul(const void* in, int dt_in, void* out, int dt_out, int T, int F, void* stream) {
   if (!in || !out || T <= 0 || F <= 0 || bad_dt(dt_in) || bad_dt(dt_out)) return failf(KB2SEQ_ERR_VALUE, "act_mul: bad argument");
-  const long long n = (long long)T * F;
-  act_mul_kernel<<<(unsigned)((n + 255) / 256), 256, 0, (cudaStream_t)stream>>>(in, dt_in, out, dt_out, T, F);
+  if (T > 65535) return failf(KB2SEQ_ERR_VALUE, "act_mul: more than 65535 rows in one step");
+  if (dt_in == 1 && dt_out == 1 && F % 8 == 0 && !((uintptr_t)in & 15) && !((uintptr_t)out & 15))
+    act_mul_bf16x8_kernel<<<dim3((F / 8 + 127) / 128, T), 128, 0, (cudaStream_t)stream>>>((const bf16*)in, (bf16*)out, F);
+  else
+    act_mul_kernel<<<dim3((F + 255) / 256, T), 256, 0, (cudaStream_t)stream>>>(in, dt_in, out, dt_out, T, F);
   SEQ_LAUNCHED();
   return KB2SEQ_OK;
 }
@@ -1000,8 +1016,8 @@ KB2SEQ_API int kb2_seq_conv_silu(const float* proj, long long ldp, int T, int S,
                                  const int* seq_of, const int* cu, const int* slots, float* out, void* stream) {
   if (!proj || !taps || !tail || !seq_of || !cu || !slots || !out || T <= 0 || S <= 0 || C <= 0 || K <= 0)
     return failf(KB2SEQ_ERR_VALUE, "conv_silu: bad argument");
-  const long long n = (long long)T * C;
-  conv_silu_kernel<<<(unsigned)((n + 255) / 256), 256, 0, (cudaStream_t)stream>>>(proj, ldp, C, K, taps, tail, seq_of, cu, slots, T, out);
+  if (T > 65535) return failf(KB2SEQ_ERR_VALUE, "conv_silu: more than 65535 rows in one step");
+  conv_silu_kernel<<<dim3((C + 255) / 256, T), 256, 0, (cudaStream_t)stream>>>(proj, ldp, C, K, taps, tail, seq_of, cu, slots, T, out);
   SEQ_LAUNCHED();
   if (K > 1) {
     const long long m = (long long)S * C;
