@@ -203,7 +203,7 @@ template <> __device__ __forceinline__ void load8<bf16>(const bf16* p, float* f)
 
 // A warp owns CPW neighbouring output columns: the rows of A it loads (L1 hits after the first warp) serve CPW weight rows, and CPW
 // 16-byte weight loads per lane are in flight at once.
-template <typename TA, typename TC, int MR, int CPW>
+template <typename TA, typename TC, int MR, int CPW, int KS>
 __global__ void __launch_bounds__(256) gemv_nt_vec_kernel(const TA* __restrict__ A, long long lda, const bf16* __restrict__ B, long long ldb,
                                                           TC* __restrict__ C, long long ldc, int M, int N, int K, long long sA,
                                                           long long sB, long long sC) {
@@ -211,17 +211,25 @@ __global__ void __launch_bounds__(256) gemv_nt_vec_kernel(const TA* __restrict__
   B += (long long)blockIdx.z * sB;
   C += (long long)blockIdx.z * sC;
   const int lane = threadIdx.x & 31;
-  const int n0 = (blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5)) * CPW;
-  if (n0 >= N) return;
+  const int group = (blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5)) / KS, kpart = (threadIdx.x >> 5) % KS;
+  const int n0 = group * CPW;
+  if (KS == 1 && n0 >= N) return;            // with K split over warps every warp stays for the block barrier
   float acc[MR][CPW];
 #pragma unroll
   for (int m = 0; m < MR; ++m)
 #pragma unroll
     for (int c = 0; c < CPW; ++c) acc[m][c] = 0.f;
-  for (int k = lane * 8; k < K; k += 256) {
-    uint4 wv[CPW];
+  // KS warps share a column group and take interleaved 256-element pieces of K; the weights of the next piece are requested before
+  // the current ones are used
+  const int kstep = 256 * KS;
+  uint4 wv[CPW], wn[CPW];
+  int k = (kpart * 32 + lane) * 8;
 #pragma unroll
-    for (int c = 0; c < CPW; ++c) wv[c] = (n0 + c < N) ? *reinterpret_cast<const uint4*>(B + (long long)(n0 + c) * ldb + k) : make_uint4(0, 0, 0, 0);
+  for (int c = 0; c < CPW; ++c) wv[c] = (k < K && n0 + c < N) ? *reinterpret_cast<const uint4*>(B + (long long)(n0 + c) * ldb + k) : make_uint4(0, 0, 0, 0);
+  for (; k < K; k += kstep) {
+    const int kn = k + kstep;
+#pragma unroll
+    for (int c = 0; c < CPW; ++c) wn[c] = (kn < K && n0 + c < N) ? *reinterpret_cast<const uint4*>(B + (long long)(n0 + c) * ldb + kn) : make_uint4(0, 0, 0, 0);
 #pragma unroll
     for (int m = 0; m < MR; ++m)
       if (m < M) {
@@ -235,6 +243,27 @@ __global__ void __launch_bounds__(256) gemv_nt_vec_kernel(const TA* __restrict__
           for (int i = 0; i < 8; ++i) acc[m][c] = fmaf(a[i], w[i], acc[m][c]);
         }
       }
+#pragma unroll
+    for (int c = 0; c < CPW; ++c) wv[c] = wn[c];
+  }
+  if constexpr (KS > 1) {
+    __shared__ float red[8][MR * CPW];
+    const int warp = threadIdx.x >> 5;
+#pragma unroll
+    for (int m = 0; m < MR; ++m)
+#pragma unroll
+      for (int c = 0; c < CPW; ++c) {
+        const float v = warp_sum(acc[m][c]);
+        if (lane == 0) red[warp][m * CPW + c] = v;
+      }
+    __syncthreads();
+    if (kpart == 0 && lane < MR * CPW) {
+      const int m = lane / CPW, c = lane % CPW;
+      float v = 0.f;
+      for (int p = 0; p < KS; ++p) v += red[warp + p][lane];
+      if (m < M && n0 + c < N) stf(C, (long long)m * ldc + n0 + c, v);
+    }
+    return;
   }
 #pragma unroll
   for (int m = 0; m < MR; ++m)
@@ -250,17 +279,20 @@ static bool launch_gemv_vec(const void* A, long long lda, const void* B, long lo
                             int batch, long long sA, long long sB, long long sC, cudaStream_t s) {
   const bool a16 = sizeof(TA) == 2;
   if (K % 8 || ldb % 8 || sB % 8 || ((uintptr_t)B & 15) || ((uintptr_t)A & 15) || lda % (a16 ? 8 : 4) || sA % (a16 ? 8 : 4)) return false;
-  // columns per warp: 4 where that still leaves two blocks per SM, else fewer
+  // columns per warp: 4 where that still leaves two blocks per SM; few columns: one per warp group, K split over 4 warps
   const long long warps = (long long)N * batch;
   if (warps >= 4 * 8 * 296) {
     dim3 grid((N + 31) / 32, 1, batch);
-    gemv_nt_vec_kernel<TA, TC, 8, 4><<<grid, 256, 0, s>>>((const TA*)A, lda, (const bf16*)B, ldb, (TC*)C, ldc, M, N, K, sA, sB, sC);
+    gemv_nt_vec_kernel<TA, TC, 8, 4, 1><<<grid, 256, 0, s>>>((const TA*)A, lda, (const bf16*)B, ldb, (TC*)C, ldc, M, N, K, sA, sB, sC);
   } else if (warps >= 2 * 8 * 296) {
     dim3 grid((N + 15) / 16, 1, batch);
-    gemv_nt_vec_kernel<TA, TC, 8, 2><<<grid, 256, 0, s>>>((const TA*)A, lda, (const bf16*)B, ldb, (TC*)C, ldc, M, N, K, sA, sB, sC);
+    gemv_nt_vec_kernel<TA, TC, 8, 2, 1><<<grid, 256, 0, s>>>((const TA*)A, lda, (const bf16*)B, ldb, (TC*)C, ldc, M, N, K, sA, sB, sC);
+  } else if (K >= 2048) {
+    dim3 grid((N + 1) / 2, 1, batch);
+    gemv_nt_vec_kernel<TA, TC, 8, 1, 4><<<grid, 256, 0, s>>>((const TA*)A, lda, (const bf16*)B, ldb, (TC*)C, ldc, M, N, K, sA, sB, sC);
   } else {
     dim3 grid((N + 7) / 8, 1, batch);
-    gemv_nt_vec_kernel<TA, TC, 8, 1><<<grid, 256, 0, s>>>((const TA*)A, lda, (const bf16*)B, ldb, (TC*)C, ldc, M, N, K, sA, sB, sC);
+    gemv_nt_vec_kernel<TA, TC, 8, 1, 1><<<grid, 256, 0, s>>>((const TA*)A, lda, (const bf16*)B, ldb, (TC*)C, ldc, M, N, K, sA, sB, sC);
   }
   return true;
 }
@@ -734,9 +766,10 @@ __global__ void __launch_bounds__(1024) delta_rule_kernel(const float* __restric
 
 // ---- the same recurrence for key sizes 32 / 64 / 128 and value sizes that are multiples of 32: state in registers.
 // delta_prep: unit-norm q (times dk^-1/2) and k per (token, key head), write strength and decay per (token, head), all tokens in
-// parallel.  delta_rule_reg: one block per (sequence, head, 32 value columns); a column's DK state entries live in the registers of
-// four adjacent lanes (DK / 4 each), the two dot products per token are finished with two shuffles; q / k / v / gates of the next 16
-// tokens stream into shared memory with cp.async while the current 16 are processed.  delta_out: per-head RMS norm and SiLU gate.
+// parallel.  delta_rule_reg: one block per (sequence, head, 32 value columns); lane = column, warp p holds rows [p DK/8, (p+1) DK/8) of
+// the state in registers, so the k and q values a warp needs are the same for all its lanes (one shared-memory transaction per 16
+// bytes); the pieces of S^T k meet through shared memory and one block barrier per token, those of S^T q once per 8 tokens; q / k / v /
+// gates of the next 8 tokens stream into shared memory with cp.async while the current 8 are processed.  delta_out: per-head RMS norm and SiLU gate.
 __global__ void __launch_bounds__(256) delta_prep_kernel(const float* __restrict__ conv, int C, const float* __restrict__ proj,
                                                          long long ldp, int a_off, int b_off, int H, int Hk, int dk,
                                                          const float* __restrict__ A_log, const float* __restrict__ dt_bias, long long T,
@@ -780,39 +813,41 @@ __device__ __forceinline__ void cp_async4(void* smem_dst, const void* gmem_src) 
 __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
 __device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_group 0;" ::: "memory"); }
 
-constexpr int kRegTile = 16;
+constexpr int kRegTile = 8;
+constexpr int kRegPieces = 8;                // warps of a block (the sum of the pieces below is written for 8): warp p holds rows [p DK/8, (p+1) DK/8) of 32 state columns
 template <int DK>
-__global__ void __launch_bounds__(128) delta_rule_reg_kernel(const float* __restrict__ qn, const float* __restrict__ kn,
-                                                             const float* __restrict__ conv, int C, int v_col0,
-                                                             const float* __restrict__ beta, const float* __restrict__ dec, int H, int Hk,
-                                                             int dv, float* __restrict__ state, const int* __restrict__ cu,
-                                                             const int* __restrict__ slots, float* __restrict__ o_out) {
-  constexpr int Q = DK / 4;                 // state rows per lane
-  constexpr int RS = 4 * (Q + 4);           // padded q / k row in shared memory: the four quarters land in different banks
-  __shared__ __align__(16) float ks[2][kRegTile][RS];
-  __shared__ __align__(16) float qs[2][kRegTile][RS];
+__global__ void __launch_bounds__(32 * kRegPieces) delta_rule_reg_kernel(const float* __restrict__ qn, const float* __restrict__ kn,
+                                                                         const float* __restrict__ conv, int C, int v_col0,
+                                                                         const float* __restrict__ beta, const float* __restrict__ dec,
+                                                                         int H, int Hk, int dv, float* __restrict__ state,
+                                                                         const int* __restrict__ cu, const int* __restrict__ slots,
+                                                                         float* __restrict__ o_out) {
+  constexpr int P = kRegPieces, NT = 32 * P;
+  constexpr int Q = DK / P;                 // state rows per thread
+  __shared__ __align__(16) float ks[2][kRegTile][DK];
+  __shared__ __align__(16) float qs[2][kRegTile][DK];
   __shared__ __align__(16) float vs[2][kRegTile][32];
   __shared__ float bs[2][kRegTile], gs[2][kRegTile];
-  __shared__ float os[kRegTile][33];
+  __shared__ float part[2][P][32];          // per token: the pieces of S^T k, summed by every warp after one barrier
+  __shared__ float os_part[kRegTile][P][32];   // pieces of S^T q, summed once per tile
   const int s = blockIdx.x, h = blockIdx.y, j0 = blockIdx.z * 32;
   const int hk = h / (H / Hk);
-  const int tid = threadIdx.x, quarter = tid & 3, col = tid >> 2;
+  const int tid = threadIdx.x, lane = tid & 31, piece = tid >> 5;
   const int t0 = cu[s], n = cu[s + 1] - cu[s];
   float* Sg = state + ((long long)slots[s] * H + h) * DK * dv;
   float S[Q];
 #pragma unroll
-  for (int ii = 0; ii < Q; ++ii) S[ii] = Sg[(long long)(quarter * Q + ii) * dv + j0 + col];
+  for (int ii = 0; ii < Q; ++ii) S[ii] = Sg[(long long)(piece * Q + ii) * dv + j0 + lane];
 
   auto load_tile = [&](int buf, int b0) {
     const int nt = min(kRegTile, n - b0);
-    for (int c = tid; c < nt * (DK / 4); c += 128) {                 // 16-byte chunks of the q and k rows
+    for (int c = tid; c < nt * (DK / 4); c += NT) {                  // 16-byte chunks of the q and k rows
       const int tt = c / (DK / 4), cc = c - tt * (DK / 4);
-      const int dst = (cc / (Q / 4)) * (Q + 4) + (cc % (Q / 4)) * 4;
       const long long src = ((long long)(t0 + b0 + tt) * Hk + hk) * DK + cc * 4;
-      cp_async16(&ks[buf][tt][dst], kn + src);
-      cp_async16(&qs[buf][tt][dst], qn + src);
+      cp_async16(&ks[buf][tt][cc * 4], kn + src);
+      cp_async16(&qs[buf][tt][cc * 4], qn + src);
     }
-    for (int c = tid; c < nt * 8; c += 128) {
+    for (int c = tid; c < nt * 8; c += NT) {
       const int tt = c >> 3, cc = c & 7;
       cp_async16(&vs[buf][tt][cc * 4], conv + (long long)(t0 + b0 + tt) * C + v_col0 + h * dv + j0 + cc * 4);
     }
@@ -828,51 +863,60 @@ __global__ void __launch_bounds__(128) delta_rule_reg_kernel(const float* __rest
   for (int b0 = 0; b0 < n; b0 += kRegTile, buf ^= 1) {
     const int nt = min(kRegTile, n - b0);
     cp_async_wait_all();
-    __syncthreads();                                  // tile `buf` is in place; everyone is done with the other buffer and with os
+    __syncthreads();                                  // tile `buf` is in place; everyone is done with the other buffer and with os_part
     if (b0 + kRegTile < n) load_tile(buf ^ 1, b0 + kRegTile);
     for (int tt = 0; tt < nt; ++tt) {
       const float g = gs[buf][tt], b = bs[buf][tt];
-      const float4* k4 = reinterpret_cast<const float4*>(&ks[buf][tt][quarter * (Q + 4)]);
-      const float4* q4 = reinterpret_cast<const float4*>(&qs[buf][tt][quarter * (Q + 4)]);
+      // the same address for every lane: one shared-memory transaction per 16 bytes.  All of the token's k and q values are fetched
+      // up front (the loads are in flight together, none has to wait behind the barrier below)
+      const float4* k4 = reinterpret_cast<const float4*>(&ks[buf][tt][piece * Q]);
+      const float4* q4 = reinterpret_cast<const float4*>(&qs[buf][tt][piece * Q]);
+      float4 kr[Q / 4], qr[Q / 4];
+#pragma unroll
+      for (int ii = 0; ii < Q / 4; ++ii) kr[ii] = k4[ii];
+#pragma unroll
+      for (int ii = 0; ii < Q / 4; ++ii) qr[ii] = q4[ii];
+      const float vv = vs[buf][tt][lane];
       float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
 #pragma unroll
       for (int ii = 0; ii < Q / 4; ++ii) {
-        const float4 kk = k4[ii];
-        a0 = fmaf(S[4 * ii], kk.x, a0);
-        a1 = fmaf(S[4 * ii + 1], kk.y, a1);
-        a2 = fmaf(S[4 * ii + 2], kk.z, a2);
-        a3 = fmaf(S[4 * ii + 3], kk.w, a3);
+        a0 = fmaf(S[4 * ii], kr[ii].x, a0);
+        a1 = fmaf(S[4 * ii + 1], kr[ii].y, a1);
+        a2 = fmaf(S[4 * ii + 2], kr[ii].z, a2);
+        a3 = fmaf(S[4 * ii + 3], kr[ii].w, a3);
       }
-      float sk = (a0 + a1) + (a2 + a3);
-      sk += __shfl_xor_sync(0xffffffffu, sk, 1);
-      sk += __shfl_xor_sync(0xffffffffu, sk, 2);
-      const float u = b * (vs[buf][tt][col] - g * sk);
+      part[tt & 1][piece][lane] = (a0 + a1) + (a2 + a3);
+      __syncthreads();
+      float pp[P];
+#pragma unroll
+      for (int p = 0; p < P; ++p) pp[p] = part[tt & 1][p][lane];
+      const float sk = ((pp[0] + pp[1]) + (pp[2] + pp[3])) + ((pp[4] + pp[5]) + (pp[6] + pp[7]));
+      const float u = b * (vv - g * sk);
       a0 = a1 = a2 = a3 = 0.f;
 #pragma unroll
       for (int ii = 0; ii < Q / 4; ++ii) {
-        const float4 kk = k4[ii], qq = q4[ii];
-        S[4 * ii] = fmaf(kk.x, u, g * S[4 * ii]);
-        S[4 * ii + 1] = fmaf(kk.y, u, g * S[4 * ii + 1]);
-        S[4 * ii + 2] = fmaf(kk.z, u, g * S[4 * ii + 2]);
-        S[4 * ii + 3] = fmaf(kk.w, u, g * S[4 * ii + 3]);
-        a0 = fmaf(S[4 * ii], qq.x, a0);
-        a1 = fmaf(S[4 * ii + 1], qq.y, a1);
-        a2 = fmaf(S[4 * ii + 2], qq.z, a2);
-        a3 = fmaf(S[4 * ii + 3], qq.w, a3);
+        S[4 * ii] = fmaf(kr[ii].x, u, g * S[4 * ii]);
+        S[4 * ii + 1] = fmaf(kr[ii].y, u, g * S[4 * ii + 1]);
+        S[4 * ii + 2] = fmaf(kr[ii].z, u, g * S[4 * ii + 2]);
+        S[4 * ii + 3] = fmaf(kr[ii].w, u, g * S[4 * ii + 3]);
+        a0 = fmaf(S[4 * ii], qr[ii].x, a0);
+        a1 = fmaf(S[4 * ii + 1], qr[ii].y, a1);
+        a2 = fmaf(S[4 * ii + 2], qr[ii].z, a2);
+        a3 = fmaf(S[4 * ii + 3], qr[ii].w, a3);
       }
-      float o = (a0 + a1) + (a2 + a3);
-      o += __shfl_xor_sync(0xffffffffu, o, 1);
-      o += __shfl_xor_sync(0xffffffffu, o, 2);
-      if (quarter == 0) os[tt][col] = o;
+      os_part[tt][piece][lane] = (a0 + a1) + (a2 + a3);
     }
     __syncthreads();
-    for (int i = tid; i < nt * 32; i += 128) {
+    for (int i = tid; i < nt * 32; i += NT) {
       const int tt = i >> 5, c = i & 31;
-      o_out[((long long)(t0 + b0 + tt) * H + h) * dv + j0 + c] = os[tt][c];
+      float o = 0.f;
+#pragma unroll
+      for (int p = 0; p < P; ++p) o += os_part[tt][p][c];
+      o_out[((long long)(t0 + b0 + tt) * H + h) * dv + j0 + c] = o;
     }
   }
 #pragma unroll
-  for (int ii = 0; ii < Q; ++ii) Sg[(long long)(quarter * Q + ii) * dv + j0 + col] = S[ii];
+  for (int ii = 0; ii < Q; ++ii) Sg[(long long)(piece * Q + ii) * dv + j0 + lane] = S[ii];
 }
 
 // out[t, h, :] = o / rms(o) * norm_w * silu(gate); a warp per (token, head)
@@ -1048,9 +1092,9 @@ KB2SEQ_API int kb2_seq_delta_rule(const float* conv, int C, const float* proj, l
     SEQ_LAUNCHED();
     dim3 grid(S, H, dv / 32);
     const int v_col0 = 2 * Hk * dk;
-    if (dk == 32) delta_rule_reg_kernel<32><<<grid, 128, 0, st>>>(qn, kn, conv, C, v_col0, be, de, H, Hk, dv, state, cu, slots, ob);
-    else if (dk == 64) delta_rule_reg_kernel<64><<<grid, 128, 0, st>>>(qn, kn, conv, C, v_col0, be, de, H, Hk, dv, state, cu, slots, ob);
-    else delta_rule_reg_kernel<128><<<grid, 128, 0, st>>>(qn, kn, conv, C, v_col0, be, de, H, Hk, dv, state, cu, slots, ob);
+    if (dk == 32) delta_rule_reg_kernel<32><<<grid, 32 * kRegPieces, 0, st>>>(qn, kn, conv, C, v_col0, be, de, H, Hk, dv, state, cu, slots, ob);
+    else if (dk == 64) delta_rule_reg_kernel<64><<<grid, 32 * kRegPieces, 0, st>>>(qn, kn, conv, C, v_col0, be, de, H, Hk, dv, state, cu, slots, ob);
+    else delta_rule_reg_kernel<128><<<grid, 32 * kRegPieces, 0, st>>>(qn, kn, conv, C, v_col0, be, de, H, Hk, dv, state, cu, slots, ob);
     SEQ_LAUNCHED();
     const long long no = (long long)T * H;
     delta_out_kernel<<<(unsigned)((no + 7) / 8), 256, 0, st>>>(ob, proj, ldp, g_off, H, dv, norm_w, eps, T, out, dt_out);
