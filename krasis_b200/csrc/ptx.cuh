@@ -41,12 +41,17 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
 static __device__ int g_mbar_timed_out = 0;
 __device__ __forceinline__ void mbar_wait(uint64_t* bar, uint32_t parity) {
   if (mbar_try_wait(bar, parity)) return;
-  const long long t0 = clock64();
+  uint32_t spins = 0;
+  long long t0 = 0;
   while (!mbar_try_wait(bar, parity)) {
-    if (*reinterpret_cast<volatile int*>(&g_mbar_timed_out)) return;
-    if (clock64() - t0 > 4000000000ll) {
-      *reinterpret_cast<volatile int*>(&g_mbar_timed_out) = 1;
-      return;
+    if ((++spins & 0xFFFu) == 0) {                  // the clock and the flag are looked at once per 4096 failed tries
+      if (*reinterpret_cast<volatile int*>(&g_mbar_timed_out)) return;
+      const long long now = clock64();
+      if (t0 == 0) t0 = now;
+      else if (now - t0 > 4000000000ll) {
+        *reinterpret_cast<volatile int*>(&g_mbar_timed_out) = 1;
+        return;
+      }
     }
   }
 }
