@@ -79,7 +79,14 @@ __device__ __forceinline__ float gelu_tanh(float z) {
   return 0.5f * z * (1.f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z)));
 }
 __device__ __forceinline__ float silu(float z) { return z / (1.f + expf(-z)); }
-__device__ __forceinline__ float softplus(float z) { return z > 20.f ? z : log1pf(expf(z)); }
+// Per-token decay exp(-exp(A_log) * softplus(a + dt_bias)).  A recurrent state multiplies by it at every token, so a rounding bias of
+// the fp32 exp / log1p chain (a fraction of an ulp, but of one sign) would grow linearly with the distance to a far token; evaluated in
+// fp64 and rounded once, the fp32 decay carries only its own unbiased half ulp.
+__device__ __forceinline__ float decay_of(float a_log, float a, float dt_bias) {
+  const double z = (double)a + (double)dt_bias;
+  const double sp = z > 40.0 ? z : log1p(exp(z));
+  return (float)exp(-exp((double)a_log) * sp);
+}
 
 __device__ __forceinline__ float warp_sum(float v) {
 #pragma unroll
@@ -700,7 +707,7 @@ __global__ void __launch_bounds__(1024) delta_rule_kernel(const float* __restric
   const int t0 = cu[s], n = cu[s + 1] - cu[s];
   float* Sg = state + ((long long)slots[s] * H + h) * dk * dv;
   for (int i = tid; i < dk * dv; i += blockDim.x) S[i] = Sg[i];
-  const float a_neg = -expf(A_log[h]), bias = dt_bias[h], qscale = rsqrtf((float)dk);
+  const float a_log_h = A_log[h], bias = dt_bias[h], qscale = 1.f / sqrtf((float)dk);
   const int q_col = hk * dk, k_col = Hk * dk + hk * dk, v_col = 2 * Hk * dk + h * dv;
   for (int b0 = 0; b0 < n; b0 += kDeltaTile) {
     const int nt = min(kDeltaTile, n - b0);
@@ -723,7 +730,7 @@ __global__ void __launch_bounds__(1024) delta_rule_kernel(const float* __restric
       if (lane == 0) {
         const float* pr = proj + (long long)(t0 + b0 + tt) * ldp;
         beta[tt] = 1.f / (1.f + expf(-pr[b_off + h]));
-        dec[tt] = expf(a_neg * softplus(pr[a_off + h] + bias));
+        dec[tt] = decay_of(a_log_h, pr[a_off + h], bias);
       }
     }
     __syncthreads();
@@ -790,7 +797,7 @@ __global__ void __launch_bounds__(256) delta_prep_kernel(const float* __restrict
   }
   sq = warp_sum(sq);
   sk = warp_sum(sk);
-  const float rq = rsqrtf((float)dk) / sqrtf(sq + 1e-6f), rk = 1.f / sqrtf(sk + 1e-6f);
+  const float rq = (1.f / sqrtf((float)dk)) / sqrtf(sq + 1e-6f), rk = 1.f / sqrtf(sk + 1e-6f);
   for (int i = lane; i < dk; i += 32) {
     qn[w * dk + i] = row[q_col + i] * rq;
     kn[w * dk + i] = row[k_col + i] * rk;
@@ -800,7 +807,7 @@ __global__ void __launch_bounds__(256) delta_prep_kernel(const float* __restrict
     const int h = hk * rep + lane;
     const float* pr = proj + t * ldp;
     beta[t * H + h] = 1.f / (1.f + expf(-pr[b_off + h]));
-    dec[t * H + h] = expf(-expf(A_log[h]) * softplus(pr[a_off + h] + dt_bias[h]));
+    dec[t * H + h] = decay_of(A_log[h], pr[a_off + h], dt_bias[h]);
   }
 }
 
