@@ -201,6 +201,12 @@ __global__ void __launch_bounds__(256) gemv_nt_kernel(const TA* __restrict__ A, 
   }
 }
 
+// streamed once: keep the weights out of L1 so that the few activation rows every warp re-reads stay there
+__device__ __forceinline__ uint4 ld_stream16(const void* p) {
+  uint4 v;
+  asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
+  return v;
+}
 template <typename TA> __device__ __forceinline__ void load8(const TA* p, float* f);
 template <> __device__ __forceinline__ void load8<float>(const float* p, float* f) {
   const float4 a = *reinterpret_cast<const float4*>(p), b = *reinterpret_cast<const float4*>(p + 4);
@@ -232,11 +238,11 @@ __global__ void __launch_bounds__(256) gemv_nt_vec_kernel(const TA* __restrict__
   uint4 wv[CPW], wn[CPW];
   int k = (kpart * 32 + lane) * 8;
 #pragma unroll
-  for (int c = 0; c < CPW; ++c) wv[c] = (k < K && n0 + c < N) ? *reinterpret_cast<const uint4*>(B + (long long)(n0 + c) * ldb + k) : make_uint4(0, 0, 0, 0);
+  for (int c = 0; c < CPW; ++c) wv[c] = (k < K && n0 + c < N) ? ld_stream16(B + (long long)(n0 + c) * ldb + k) : make_uint4(0, 0, 0, 0);
   for (; k < K; k += kstep) {
     const int kn = k + kstep;
 #pragma unroll
-    for (int c = 0; c < CPW; ++c) wn[c] = (kn < K && n0 + c < N) ? *reinterpret_cast<const uint4*>(B + (long long)(n0 + c) * ldb + kn) : make_uint4(0, 0, 0, 0);
+    for (int c = 0; c < CPW; ++c) wn[c] = (kn < K && n0 + c < N) ? ld_stream16(B + (long long)(n0 + c) * ldb + kn) : make_uint4(0, 0, 0, 0);
 #pragma unroll
     for (int m = 0; m < MR; ++m)
       if (m < M) {
@@ -286,21 +292,22 @@ static bool launch_gemv_vec(const void* A, long long lda, const void* B, long lo
                             int batch, long long sA, long long sB, long long sC, cudaStream_t s) {
   const bool a16 = sizeof(TA) == 2;
   if (K % 8 || ldb % 8 || sB % 8 || ((uintptr_t)B & 15) || ((uintptr_t)A & 15) || lda % (a16 ? 8 : 4) || sA % (a16 ? 8 : 4)) return false;
-  // columns per warp: 4 where that still leaves two blocks per SM; few columns: one per warp group, K split over 4 warps
+  // columns per warp: 4 where that still leaves two blocks per SM; few columns: one per warp group, K split over 4 warps.
+  // Up to 4 rows run the 4-row instantiation (half the accumulators: more blocks per SM, more weight bytes in flight).
   const long long warps = (long long)N * batch;
+#define KB2_GEMV(MRV, CPWV, KSV, GX)                                                                                        \
+  gemv_nt_vec_kernel<TA, TC, MRV, CPWV, KSV><<<dim3(GX, 1, batch), 256, 0, s>>>((const TA*)A, lda, (const bf16*)B, ldb, (TC*)C, ldc, M, N, K, \
+                                                                                sA, sB, sC)
   if (warps >= 4 * 8 * 296) {
-    dim3 grid((N + 31) / 32, 1, batch);
-    gemv_nt_vec_kernel<TA, TC, 8, 4, 1><<<grid, 256, 0, s>>>((const TA*)A, lda, (const bf16*)B, ldb, (TC*)C, ldc, M, N, K, sA, sB, sC);
+    if (M <= 4) KB2_GEMV(4, 4, 1, (N + 31) / 32); else KB2_GEMV(8, 4, 1, (N + 31) / 32);
   } else if (warps >= 2 * 8 * 296) {
-    dim3 grid((N + 15) / 16, 1, batch);
-    gemv_nt_vec_kernel<TA, TC, 8, 2, 1><<<grid, 256, 0, s>>>((const TA*)A, lda, (const bf16*)B, ldb, (TC*)C, ldc, M, N, K, sA, sB, sC);
+    if (M <= 4) KB2_GEMV(4, 2, 1, (N + 15) / 16); else KB2_GEMV(8, 2, 1, (N + 15) / 16);
   } else if (K >= 2048) {
-    dim3 grid((N + 1) / 2, 1, batch);
-    gemv_nt_vec_kernel<TA, TC, 8, 1, 4><<<grid, 256, 0, s>>>((const TA*)A, lda, (const bf16*)B, ldb, (TC*)C, ldc, M, N, K, sA, sB, sC);
+    if (M <= 4) KB2_GEMV(4, 1, 4, (N + 1) / 2); else KB2_GEMV(8, 1, 4, (N + 1) / 2);
   } else {
-    dim3 grid((N + 7) / 8, 1, batch);
-    gemv_nt_vec_kernel<TA, TC, 8, 1, 1><<<grid, 256, 0, s>>>((const TA*)A, lda, (const bf16*)B, ldb, (TC*)C, ldc, M, N, K, sA, sB, sC);
+    if (M <= 4) KB2_GEMV(4, 1, 1, (N + 7) / 8); else KB2_GEMV(8, 1, 1, (N + 7) / 8);
   }
+#undef KB2_GEMV
   return true;
 }
 
