@@ -810,8 +810,8 @@ __global__ void __launch_bounds__(256) delta_prep_kernel(const float* __restrict
     kn[w * dk + i] = row[k_col + i] * rk;
   }
   const int rep = H / Hk;
-  if (lane < rep) {
-    const int h = hk * rep + lane;
+  for (int j = lane; j < rep; j += 32) {
+    const int h = hk * rep + j;
     const float* pr = proj + t * ldp;
     beta[t * H + h] = 1.f / (1.f + expf(-pr[b_off + h]));
     dec[t * H + h] = decay_of(A_log[h], pr[a_off + h], dt_bias[h]);
