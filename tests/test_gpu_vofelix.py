@@ -194,7 +194,8 @@ def test_latent_attention_alone(seq, mixer):
                                    delta_cfg(heads=2, kv_heads=2, dim=16, vdim=72, conv=5),
                                    # key sizes 32 / 64 / 128 with value sizes in multiples of 32 run the register-state kernels
                                    delta_cfg(heads=2, kv_heads=1, dim=32, vdim=32, conv=3), delta_cfg(heads=3, kv_heads=3, dim=64, vdim=64, conv=4),
-                                   delta_cfg(heads=2, kv_heads=2, dim=128, vdim=96, conv=2)])
+                                   delta_cfg(heads=2, kv_heads=2, dim=128, vdim=96, conv=2),
+                                   delta_cfg(heads=66, kv_heads=2, dim=32, vdim=32, conv=2)])      # 33 heads share a key head
 def test_delta_mixer_alone(seq, mixer):
     raw = _one_layer("delta", mixer)
     model, w = build(raw, seed=12)
@@ -489,4 +490,42 @@ def test_registry_loads_a_checkpoint_directory(seq, tmp_path):
     assert architecture_of(str(tmp_path)) == "Vofelix"
     model = load_model(str(tmp_path), dtype=torch.float32)
     tk = toks(25, 50, 14)
-    close(run_portions(model, tk, [25]), O.forward(raw, {k: v.numpy().astype(np.float64) for k, v in w.items()}, tk), 4e-5, "loaded checkpoint")
+    w64 = {k: v.numpy().astype(np.float64) for k, v in w.items()}
+    want = O.forward(raw, w64, tk)
+    close(run_portions(model, tk, [25]), want, 4e-5, "loaded checkpoint")
+
+    # the trace runner on the same directory: steps from standard input, logits of the wanted places to <step>.f32, "done <step>" lines
+    import io
+    import sys
+    from krasis_b200 import trace_runner
+    steps = [{"step": 0, "entries": [{"id": "x", "tokens": tk[:10], "want": [0, 9]}, {"id": "y", "tokens": tk[:3], "want": []}], "end": []},
+             {"step": 1, "entries": [{"id": "y", "tokens": tk[3:4], "want": []}], "end": ["y"]},
+             {"step": 2, "entries": [{"id": "x", "tokens": tk[10:25], "want": [14]}, {"id": "z", "tokens": tk[:2], "want": [1]}], "end": ["x", "z"]}]
+    out_dir = tmp_path / "out"
+    stdin, stdout = sys.stdin, sys.stdout
+    sys.stdin, sys.stdout = io.StringIO("".join(json.dumps(x) + "\n" for x in steps)), io.StringIO()
+    try:
+        rc = trace_runner.main(["--model", str(tmp_path), "--dtype", "float32", "--out", str(out_dir), "--max-tokens", "128"])
+        printed = sys.stdout.getvalue()
+    finally:
+        sys.stdin, sys.stdout = stdin, stdout
+    assert rc == 0 and [l for l in printed.splitlines() if l.startswith("done")] == ["done 0", "done 1", "done 2"]
+    assert not (out_dir / "1.f32").exists()
+    got0 = np.fromfile(out_dir / "0.f32", dtype="<f4").reshape(2, -1)
+    got2 = np.fromfile(out_dir / "2.f32", dtype="<f4").reshape(2, -1)
+    close(got0, want[[0, 9]], 4e-5, "trace step 0")
+    close(got2, np.stack([want[24], want[1]]), 4e-5, "trace step 2")
+
+    # the generation command line: greedy ids for two prompts, one JSON line each
+    from krasis_b200.__main__ import main as cli
+    sys.stdout = io.StringIO()
+    try:
+        rc = cli(["generate", "--model", str(tmp_path), "--dtype", "float32", "--prompt-ids", ",".join(map(str, tk[:7])), "--prompt-ids", "3,4",
+                  "--max-new-tokens", "3", "--max-tokens", "256"])
+        lines = [json.loads(l) for l in sys.stdout.getvalue().splitlines() if l.startswith("{")]
+    finally:
+        sys.stdout = stdout
+    assert rc == 0 and [x["prompt_tokens"] for x in lines] == [7, 2] and all(len(x["generated"]) == 3 for x in lines)
+    first = O.forward(raw, w64, tk[:7])[-1]
+    if np.sort(first)[-1] - np.sort(first)[-2] > 1e-3 * np.abs(first).max():
+        assert lines[0]["generated"][0] == int(np.argmax(first))
