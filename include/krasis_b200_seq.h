@@ -79,6 +79,67 @@ KB2SEQ_API int kb2_seq_delta_rule(const float* conv, int C, const float* proj, l
                                   float eps, float* state, const int* cu, const int* slots, float* scratch, void* out, int dt_out,
                                   void* stream);
 
+/* ---- second part (csrc/seq_mix.cu): per-head key/value caches, multi-map attention, gated linear units, routed experts ---- */
+
+/* x += (y + y2) in that order (y2 may be null: x += y); h = layer_norm(x; wb, bb), bb may be null (no bias), h may be null */
+KB2SEQ_API int kb2_seq_residual_add_norm(float* x, const float* y, const float* y2, const float* wb, const float* bb, void* h, int dt_h,
+                                         int T, int W, float eps, void* stream);
+
+/* proj [T, ldp] fp32 = [q: H x M x d | k: G x M x d | v: G x dv | ...]: H query heads with M maps each, G key/value heads (0: the layer
+ * reads another layer's cache).  bias (same column order, may be null) is added; every q / k vector of d is RMS-normed with the weight
+ * qw / kw [d] (null: no norm) and its first rot_dims dimensions are rotated as interleaved pairs by position * freq[i].  q is written
+ * back in place; k [G M d] and v [G dv] go to the cache rows of the tokens' positions. */
+KB2SEQ_API int kb2_seq_head_kv_prep(float* proj, long long ldp, int T, int H, int G, int M, int d, int dv, const float* bias,
+                                    const float* qw, const float* kw, float eps, const double* freq, int rot_dims, const int* positions,
+                                    const int* seq_of, const int* pages, int max_pages, int page_size, void* kc, void* vc, int dt_cache,
+                                    void* stream);
+
+/* out [T, H, M, dv] fp32: softmax attention of each (head, map) query over the keys j <= pos of its sequence that lie in the same
+ * chunk (chunk > 0: floor(j / chunk) == floor(pos / chunk)) and within 0 <= pos - j < window.  Head h reads key/value head h / (H / G);
+ * map m reads the keys of map m; all maps read the same values.  cu / skip_from and nsplit / part_acc [T H M][nsplit][dv] /
+ * part_ml [T H M][nsplit][2] as in kb2_seq_latent_window_attn, except that the pieces are merged by kb2_seq_attn_finish. */
+KB2SEQ_API int kb2_seq_paged_attn(const float* proj, long long ldp, int T, int H, int G, int M, int d, int dv, const void* kc,
+                                  const void* vc, int dt_cache, const int* positions, const int* seq_of, const int* pages, int max_pages,
+                                  int page_size, float scale, int chunk, int window, float* out, int nsplit, float* part_acc,
+                                  float* part_ml, const int* cu, int skip_from, void* stream);
+
+/* out[t, h, :] = f * sum_m coef[m] a[t, h, m, :] (coef null: ones), f = post_scale / rms(sum) if unit_norm, times sigmoid(gate[t * ldg + h])
+ * if gate is given.  nsplit > 1: a is merged from part_acc / part_ml first. */
+KB2SEQ_API int kb2_seq_attn_finish(const float* a, const float* part_acc, const float* part_ml, int nsplit, int T, int H, int M, int dv,
+                                   const float* coef, int unit_norm, float eps, float post_scale, const float* gate, long long ldg,
+                                   void* out, int dt_out, const int* seq_of, const int* cu, int skip_from, void* stream);
+
+/* in [rows, ld_in] = [gate: F | up: F]; out [rows, F].  kind 0: gelu_tanh(g) u, 1: silu(g) u, 2: g' sigmoid(alpha g') (u' + 1) with
+ * g' = min(g, limit), u' = clamp(u, -limit, limit).  n_tiles (device, may be null): only n_tiles[0] * tile_rows rows are computed. */
+KB2SEQ_API int kb2_seq_glu(const void* in, int dt_in, long long ld_in, void* out, int dt_out, long long rows, int F, int kind, float limit,
+                           float alpha, const int* n_tiles, int tile_rows, void* stream);
+
+/* Router: z [T, ldz] fp32 logits of E outputs -> ids [T, top], weights [T, top].  score_kind 0 softmax, 1 sigmoid; choice = score +
+ * correction (may be null); groups > 1: E / groups neighbours form a group, only the `keep` groups with the largest maximal choice can
+ * be chosen; weights are the chosen scores (without correction), divided by their sum if renorm, times out_scale. */
+KB2SEQ_API int kb2_seq_route(const float* z, long long ldz, int T, int E, const float* correction, int score_kind, int groups, int keep,
+                             int top, int renorm, float out_scale, int* ids, float* weights, void* stream);
+
+/* Routed experts.  moe_bin: slots = T * top entries of ids; ids outside [0, E) are left out (identity experts).  Each expert's slots
+ * form a run of rows padded to whole tiles of kb2_seq_moe_tile_rows(): offs [E + 1], tile_expert [max_rows / tile], n_tiles [1],
+ * slot_row [max_rows] (row -> slot, -1 padding), pos_of_slot [slots] (slot -> row, -1 left out); counts, cursor [E] are scratch;
+ * max_rows >= slots + E * (tile - 1). */
+KB2SEQ_API int kb2_seq_moe_tile_rows(void);
+KB2SEQ_API int kb2_seq_moe_bin(const int* ids, long long slots, int E, int* counts, int* offs, int* cursor, int* tile_expert, int* n_tiles,
+                               int* slot_row, long long max_rows, int* pos_of_slot, void* stream);
+/* C[p, :] = A[src(p), :] * B[tile_expert[p / tile]]^T (B: [experts][N][ldb], expert stride sB) for the rows of the first n_tiles[0] tiles;
+ * src(p) = p, or row_map[p] / div when row_map is given (negative: zeros). */
+KB2SEQ_API int kb2_seq_moe_gemm(const void* A, int dtA, long long lda, const int* row_map, int div, const void* B, int dtB, long long ldb,
+                                long long sB, void* C, int dtC, long long ldc, int N, int K, const int* tile_expert, const int* n_tiles,
+                                int max_tiles, void* stream);
+/* Few slots, no binning: C[slot, :] = A[slot / div, :] * B[ids[slot]]^T; slots with ids outside [0, E) are skipped. */
+KB2SEQ_API int kb2_seq_moe_gemv(const void* A, int dtA, long long lda, int div, const int* ids, int E, const void* B, int dtB, long long ldb,
+                                long long sB, void* C, int dtC, long long ldc, int slots, int N, int K, void* stream);
+/* out[t, :] = sum_k weights[t, k] * (y[row of slot (t, k)] | h[t] if E <= ids < E + ident) + shared[t] (may be null); pos_of_slot null:
+ * the row of a slot is the slot itself. */
+KB2SEQ_API int kb2_seq_moe_combine(const float* y, const int* pos_of_slot, const int* ids, const float* weights, int T, int top, int E,
+                                   int ident, const void* h, int dt_h, const float* shared, float* out, int W, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -438,6 +438,26 @@ class LatentKVCache(PagedKVCache):
         return self.ckv[layer_offset], self.kr[layer_offset]
 
 
+class HeadKVCache(PagedKVCache):
+    """Paged cache of per-head keys and values for several live sequences: per caching layer one pool of keys
+    [max_pages, page_size, key_width] (all key/value heads and maps of a token side by side, after norm and rotation) and one of values
+    [max_pages, page_size, value_width], in the serving dtype (bfloat16 or float32).  Layers may differ in their widths and share one
+    page numbering; a layer that reads another layer's keys and values is given that layer's pools (`layer_offset` of the source).
+    Allocation is the free list of `PagedKVCache`."""
+
+    def __init__(self, layer_dims, device, max_pages: int, dtype=torch.bfloat16, page_size: int = 64):
+        if dtype not in (torch.bfloat16, torch.float32):
+            raise ValueError("cache dtype: bfloat16 or float32")
+        self.num_layers, self.page_size, self.kv_dtype, self.max_pages = len(layer_dims), page_size, dtype, max_pages
+        self.device = torch.device(device)
+        self.k = [torch.zeros((max_pages, page_size, kw), dtype=dtype, device=self.device) for kw, _ in layer_dims]
+        self.v = [torch.zeros((max_pages, page_size, vw), dtype=dtype, device=self.device) for _, vw in layer_dims]
+        self._free = list(range(max_pages - 1, -1, -1))
+
+    def get_layer_caches(self, layer_offset: int):
+        return self.k[layer_offset], self.v[layer_offset]
+
+
 class RecurrentStatePool:
     """State slots of recurrent mixers for several live sequences.  A slot is one index into every registered tensor
     ([slots, ...] fp32, one per recurrent layer run); `alloc()` hands out a zeroed slot, `free()` returns it for reuse."""

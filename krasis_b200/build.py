@@ -2,8 +2,9 @@
 
 Two targets, so that a model only compiles what it runs on:
   "core"  libkrasis_b200.so       MoE prefill path: grouped / dense tcgen05 GEMMs, Gated DeltaNet, GQA / MLA attention, NCCL glue
-  "seq"   libkrasis_b200_seq.so   ragged-batch sequence operators (csrc/seq_ops.cu): norms, generic GEMM, windowed latent
-                                  attention with a sink, short convolution + gated delta rule with state slots
+  "seq"   libkrasis_b200_seq.so   ragged-batch sequence operators (csrc/seq_ops.cu, seq_mix.cu): norms, generic GEMM, windowed latent
+                                  attention with a sink, short convolution + gated delta rule with state slots, per-head paged
+                                  multi-map attention, gated linear units, router and routed experts
 nvcc cross-compiles without a GPU.  The .so files are git-ignored; a missing or stale one is rebuilt on demand.
 """
 import hashlib
@@ -16,7 +17,7 @@ CSRC = os.path.join(HERE, "csrc")
 LIBDIR = os.path.join(HERE, "_lib")
 LIB = os.path.join(LIBDIR, "libkrasis_b200.so")
 SEQ_LIB = os.path.join(LIBDIR, "libkrasis_b200_seq.so")
-SEQ_SOURCES = ["seq_ops.cu"]
+SEQ_SOURCES = ["seq_ops.cu", "seq_mix.cu"]
 SOURCES = ["grouped_gemm.cu", "router_gemm.cu", "dense_gemm.cu", "gdn.cu", "gdn_tc.cu", "gqa.cu", "elementwise.cu", "moe_kernels.cu", "capi.cu", "capi_attn.cu", "capi_comm.cu"]
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
@@ -31,7 +32,7 @@ def _stamp(sources=None, header="krasis_b200.h"):
         for f in sorted(files):
             if sources is None and f in SEQ_SOURCES:
                 continue                      # the core library does not depend on the sequence operators
-            if sources is not None and f not in sources:
+            if sources is not None and f not in sources and not (f.endswith(".cuh") and f.startswith("seq_")):
                 continue
             h.update(open(os.path.join(root, f), "rb").read())
     h.update(open(os.path.join(HERE, "..", "include", header), "rb").read())
@@ -54,18 +55,24 @@ def _build(LIB: str, SOURCES, stamp: str, force: bool, verbose: bool) -> str:
     if not force and os.path.exists(LIB) and os.path.exists(stamp_file) and open(stamp_file).read() == stamp:
         return LIB
     nvcc = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")
-    objs = []
-    for src in SOURCES:
+    objs, procs = [], []
+    for src in SOURCES:                       # the translation units compile side by side
         obj = os.path.join(LIBDIR, src.replace(".cu", ".o"))
         cmd = [nvcc, "-c", os.path.join(CSRC, src), "-o", obj] + NVCC_FLAGS
-        r = subprocess.run(cmd, capture_output=True, text=True)
-        if verbose or r.returncode:
-            sys.stderr.write(r.stdout + r.stderr)
-        if r.returncode:
-            raise RuntimeError(f"nvcc failed on {src}")
+        procs.append((src, obj, subprocess.Popen(cmd, stdout=subprocess.PIPE, stderr=subprocess.PIPE, text=True)))
+    failed = []
+    for src, obj, proc in procs:
+        out, err = proc.communicate()
+        if verbose or proc.returncode:
+            sys.stderr.write(out + err)
+        if proc.returncode:
+            failed.append(src)
+            continue
         with open(obj + ".ptxas.txt", "w") as f:
-            f.write(r.stderr)
+            f.write(err)
         objs.append(obj)
+    if failed:
+        raise RuntimeError(f"nvcc failed on {', '.join(failed)}")
     tmp_lib = LIB + f".tmp{os.getpid()}"
     cmd = [nvcc, "-shared", "-o", tmp_lib] + objs + ["-gencode", "arch=compute_100a,code=sm_100a", "-ldl"]
     r = subprocess.run(cmd, capture_output=True, text=True)

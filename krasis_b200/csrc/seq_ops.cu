@@ -15,100 +15,12 @@
 //
 // Precision: the residual stream, every norm, softmax, the rotary angles, decays, gates and the recurrent state are fp32 (angles
 // are reduced in fp64).  `dt` codes: 0 = float32, 1 = bfloat16.
-#include <cuda_bf16.h>
-#include <cuda_runtime.h>
-#include <math.h>
-#include <stdarg.h>
-#include <stdint.h>
-#include <stdio.h>
-
-#include "../../include/krasis_b200_seq.h"
+#include "seq_common.cuh"
 
 namespace kb2seq {
 
-typedef __nv_bfloat16 bf16;
-
-static thread_local char g_err[512] = "";
-static long long g_launches = 0;
-
-static int failf(int code, const char* fmt, ...) {
-  va_list ap;
-  va_start(ap, fmt);
-  vsnprintf(g_err, sizeof(g_err), fmt, ap);
-  va_end(ap);
-  return code;
-}
-
-#define SEQ_CUDA(expr)                                                                              \
-  do {                                                                                              \
-    cudaError_t _e = (expr);                                                                        \
-    if (_e != cudaSuccess) return failf(KB2SEQ_ERR_CUDA, "%s: %s", #expr, cudaGetErrorString(_e)); \
-  } while (0)
-#define SEQ_LAUNCHED()                                                                                       \
-  do {                                                                                                       \
-    ++g_launches;                                                                                            \
-    cudaError_t _e = cudaGetLastError();                                                                     \
-    if (_e != cudaSuccess) return failf(KB2SEQ_ERR_CUDA, "launch at line %d: %s", __LINE__, cudaGetErrorString(_e)); \
-  } while (0)
-
-template <typename T> __device__ __forceinline__ float ldf(const T* p, long long i);
-template <> __device__ __forceinline__ float ldf<float>(const float* p, long long i) { return p[i]; }
-template <> __device__ __forceinline__ float ldf<bf16>(const bf16* p, long long i) { return __bfloat162float(p[i]); }
-template <typename T> __device__ __forceinline__ void stf(T* p, long long i, float v);
-template <> __device__ __forceinline__ void stf<float>(float* p, long long i, float v) { p[i] = v; }
-template <> __device__ __forceinline__ void stf<bf16>(bf16* p, long long i, float v) { p[i] = __float2bfloat16_rn(v); }
-
-__device__ __forceinline__ float ld_dt(const void* p, int dt, long long i) {
-  return dt ? __bfloat162float(((const bf16*)p)[i]) : ((const float*)p)[i];
-}
-__device__ __forceinline__ void st_dt(void* p, int dt, long long i, float v) {
-  if (dt) ((bf16*)p)[i] = __float2bfloat16_rn(v); else ((float*)p)[i] = v;
-}
-
-// eight bf16 values of one 16-byte load
-__device__ __forceinline__ void unpack8(const uint4& v, float* f) {
-  const __nv_bfloat162* p = reinterpret_cast<const __nv_bfloat162*>(&v);
-#pragma unroll
-  for (int i = 0; i < 4; ++i) {
-    const float2 t = __bfloat1622float2(p[i]);
-    f[2 * i] = t.x;
-    f[2 * i + 1] = t.y;
-  }
-}
-__device__ __forceinline__ float gelu_tanh(float z) {
-  return 0.5f * z * (1.f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z)));
-}
-__device__ __forceinline__ float silu(float z) { return z / (1.f + expf(-z)); }
-// Per-token decay exp(-exp(A_log) * softplus(a + dt_bias)).  A recurrent state multiplies by it at every token, so a rounding bias of
-// the fp32 exp / log1p chain (a fraction of an ulp, but of one sign) would grow linearly with the distance to a far token; evaluated in
-// fp64 and rounded once, the fp32 decay carries only its own unbiased half ulp.
-__device__ __forceinline__ float decay_of(float a_log, float a, float dt_bias) {
-  const double z = (double)a + (double)dt_bias;
-  const double sp = z > 40.0 ? z : log1p(exp(z));
-  return (float)exp(-exp((double)a_log) * sp);
-}
-
-__device__ __forceinline__ float warp_sum(float v) {
-#pragma unroll
-  for (int o = 16; o; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
-  return v;
-}
-__device__ __forceinline__ float warp_max(float v) {
-#pragma unroll
-  for (int o = 16; o; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
-  return v;
-}
-// sum over the block; `red` holds 32 floats; every thread gets the result
-__device__ __forceinline__ float block_sum(float v, float* red) {
-  v = warp_sum(v);
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = (blockDim.x + 31) >> 5;
-  __syncthreads();
-  if (lane == 0) red[warp] = v;
-  __syncthreads();
-  float t = 0.f;
-  for (int i = 0; i < nw; ++i) t += red[i];
-  return t;
-}
+thread_local char g_err[512] = "";
+long long g_launches = 0;
 
 // ------------------------------------------------------------------------------------------------ embedding
 template <typename T>
@@ -328,13 +240,14 @@ static void launch_gemm(const void* A, long long lda, const void* B, long long l
 
 // ------------------------------------------------------------------------------------------------ residual update + norm
 // One block per token row.  x (fp32) += norm_a(y) where norm_a is a layer norm (y_mode 1: weight wa, bias ba), an RMS norm
-// (y_mode 2: weight wa) or absent (y == nullptr); x += x0 if given; then h = layer_norm(x; wb, bb) if h is given.
+// (y_mode 2: weight wa), the plain sum y + y2 (y_mode 3: two sublayers that read the same normed input; y2 may be null) or absent
+// (y == nullptr); x += x0 if given; then h = layer_norm(x; wb, bb) if h is given (bb == nullptr: no bias).
 // Variances are means of squared deviations (two passes over the row held in shared memory).
 __global__ void __launch_bounds__(256) residual_norm_kernel(float* __restrict__ x, const float* __restrict__ y, int y_mode,
                                                             const float* __restrict__ wa, const float* __restrict__ ba,
                                                             const float* __restrict__ x0, const float* __restrict__ wb,
                                                             const float* __restrict__ bb, void* __restrict__ h, int dt_h, int W,
-                                                            float eps) {
+                                                            float eps, const float* __restrict__ y2) {
   extern __shared__ float rowbuf[];
   __shared__ float red[32];
   const long long row = blockIdx.x;
@@ -350,7 +263,17 @@ __global__ void __launch_bounds__(256) residual_norm_kernel(float* __restrict__ 
     }
     s = block_sum(s, red);
     float mean = 0.f, rstd;
-    if (y_mode == 1) {
+    if (y_mode == 3) {
+      for (int d = threadIdx.x; d < W; d += blockDim.x) {
+        float v = rowbuf[d];
+        if (y2 != nullptr) v += y2[row * W + d];
+        v += xr[d];
+        if (x0 != nullptr) v += x0[row * W + d];
+        xr[d] = v;
+        rowbuf[d] = v;
+      }
+      rstd = 0.f;
+    } else if (y_mode == 1) {
       mean = s * inv_w;
       float q = 0.f;
       for (int d = threadIdx.x; d < W; d += blockDim.x) {
@@ -362,7 +285,7 @@ __global__ void __launch_bounds__(256) residual_norm_kernel(float* __restrict__ 
     } else {
       rstd = 1.f / sqrtf(s * inv_w + eps);
     }
-    for (int d = threadIdx.x; d < W; d += blockDim.x) {
+    for (int d = threadIdx.x; y_mode != 3 && d < W; d += blockDim.x) {
       float v = (rowbuf[d] - mean) * rstd * wa[d];
       if (y_mode == 1) v += ba[d];
       v += xr[d];
@@ -391,7 +314,7 @@ __global__ void __launch_bounds__(256) residual_norm_kernel(float* __restrict__ 
   }
   q = block_sum(q, red);
   const float rstd = 1.f / sqrtf(q * inv_w + eps);
-  for (int d = threadIdx.x; d < W; d += blockDim.x) st_dt(h, dt_h, row * W + d, (rowbuf[d] - mean) * rstd * wb[d] + bb[d]);
+  for (int d = threadIdx.x; d < W; d += blockDim.x) st_dt(h, dt_h, row * W + d, (rowbuf[d] - mean) * rstd * wb[d] + (bb != nullptr ? bb[d] : 0.f));
 }
 
 // ------------------------------------------------------------------------------------------------ elementwise
@@ -428,16 +351,6 @@ __global__ void side_gate_kernel(const float* __restrict__ g, const void* __rest
 }
 
 // ------------------------------------------------------------------------------------------------ latent attention
-// Rotation angle pos * freq reduced in fp64, sin / cos in fp32.
-__device__ __forceinline__ void rot_cs(int pos, double freq, float amp, float* c, float* s) {
-  double a = (double)pos * freq;
-  a -= 6.283185307179586476925286766559 * rint(a * 0.15915494309189533576888376337251);
-  float sf, cf;
-  sincosf((float)a, &sf, &cf);
-  *c = cf * amp;
-  *s = sf * amp;
-}
-
 // proj [T, ldp] fp32 = [q (H x (dn + dr)) | latent (r) | shared rotated key (dr)].  Per token: RMS-normed latent and rotated key part
 // go to the page the token's position maps to; the query's rotated parts are rotated in place.
 __global__ void __launch_bounds__(128) latent_prep_kernel(float* __restrict__ proj, long long ldp, int H, int dn, int dr, int r,
@@ -955,8 +868,6 @@ __global__ void __launch_bounds__(256) delta_out_kernel(const float* __restrict_
 
 using namespace kb2seq;
 
-static bool bad_dt(int dt) { return dt != 0 && dt != 1; }
-
 extern "C" {
 
 KB2SEQ_API const char* kb2_seq_last_error(void) { return g_err; }
@@ -1000,7 +911,19 @@ KB2SEQ_API int kb2_seq_residual_norm(float* x, const float* y, int y_mode, const
   const size_t smem = (size_t)W * 4;
   if (smem > 200 * 1024) return failf(KB2SEQ_ERR_VALUE, "residual_norm: width %d too large", W);
   if (smem > 48 * 1024) SEQ_CUDA(cudaFuncSetAttribute(residual_norm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-  residual_norm_kernel<<<T, 256, smem, (cudaStream_t)stream>>>(x, y, y_mode, wa, ba, x0, wb, bb, h, dt_h, W, eps);
+  residual_norm_kernel<<<T, 256, smem, (cudaStream_t)stream>>>(x, y, y_mode, wa, ba, x0, wb, bb, h, dt_h, W, eps, nullptr);
+  SEQ_LAUNCHED();
+  return KB2SEQ_OK;
+}
+
+KB2SEQ_API int kb2_seq_residual_add_norm(float* x, const float* y, const float* y2, const float* wb, const float* bb, void* h, int dt_h,
+                                         int T, int W, float eps, void* stream) {
+  if (!x || T <= 0 || W <= 0 || bad_dt(dt_h) || (y2 && !y)) return failf(KB2SEQ_ERR_VALUE, "residual_add_norm: bad argument");
+  if (h && !wb) return failf(KB2SEQ_ERR_VALUE, "residual_add_norm: output norm needs its weight");
+  const size_t smem = (size_t)W * 4;
+  if (smem > 200 * 1024) return failf(KB2SEQ_ERR_VALUE, "residual_add_norm: width %d too large", W);
+  if (smem > 48 * 1024) SEQ_CUDA(cudaFuncSetAttribute(residual_norm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+  residual_norm_kernel<<<T, 256, smem, (cudaStream_t)stream>>>(x, y, 3, nullptr, nullptr, nullptr, wb, bb, h, dt_h, W, eps, y2);
   SEQ_LAUNCHED();
   return KB2SEQ_OK;
 }

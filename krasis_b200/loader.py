@@ -250,6 +250,23 @@ def _st_bf16(tensors: Dict[str, SafetensorsFile], name: str):
     raise ValueError(f"{name}: dtype {dt} cannot be loaded as a BF16 weight")
 
 
+def read_named_tensors(model_dir: str) -> dict:
+    """Every tensor of a checkpoint directory by name, on the CPU: floating-point tensors as fp32 (BF16 storage is widened exactly),
+    integer tables as they are.  For designs whose models name their tensors themselves (the model classes of the serving path)."""
+    import torch
+    files = open_model_safetensors(model_dir)
+    out = {}
+    for name, f in files.items():
+        kind = f.header[name]["dtype"]
+        if kind == "BF16":
+            out[name] = _st_bf16(files, name).float()
+        elif kind in ("F32", "F16"):
+            out[name] = torch.from_numpy(f.tensor(name).copy()).float()
+        else:
+            out[name] = torch.from_numpy(f.tensor(name).copy())
+    return out
+
+
 def norm_plus_one(w):
     """Qwen3-Next / Qwen3.5 RMSNorm weights are stored as `w - 1`: input / post-attention / final / q_norm / k_norm get
     `w + 1.0` at load, computed in BF16 (weight_loader.py:168-169,259-265,286-289); the Gated-DeltaNet gated norm does NOT

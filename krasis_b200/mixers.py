@@ -7,7 +7,14 @@ libkrasis_b200_seq (`krasis_b200.seqops`): a model composes them (krasis_b200/vo
                           with YaRN frequency blending, a sliding window and a per-head softmax sink
   GatedDeltaMixer         short causal convolutions on q / k / v, unit-norm q and k, gated delta-rule state per head in fp32
                           slots, per-head RMS norm of the read-out with a SiLU gate
-  GatedMLP                down(act(gate h) * (up h)) with the tanh form of GELU
+  MultiMapAttention       grouped-query attention over a per-head paged cache whose heads carry several attention maps (keys per
+                          map, shared values) combined with fixed coefficients (differential attention: a1 - lambda a2), with
+                          query / key RMS norm, interleaved rotary positions on part of the dimensions with linear scaling, a causal
+                          mask cut into chunks and / or a sliding window, a unit norm per head, a per-head sigmoid output gate, and
+                          optionally another layer's cached keys and values instead of projections of its own
+  GatedMLP                down(act(gate h) * (up h)): tanh-GELU, SiLU, or the clamped swish form g' sigmoid(a g') (u' + 1)
+  RoutedExperts           softmax / sigmoid router with a choice correction, expert groups and identity experts, top-k SiLU experts
+                          (binned tile GEMMs; a GEMV form for steps of few tokens) plus an optional shared expert
   TokenSideInput          per-layer token table slice, gated by a projection of the residual stream, RMS-normed
 `lin(a, w, out_dtype)` picks the GEMM: the tcgen05 kernel of the core library for large aligned bf16 products, the generic
 kernel of the sequence library otherwise (any shape, fp32 or bf16).
@@ -189,14 +196,179 @@ class GatedDeltaMixer:
 
 
 class GatedMLP:
-    """weights: gate, up [F, W], down [W, F]."""
+    """weights: gate, up [F, W], down [W, F].  act: "gelu_tanh" (gelu(g) u), "silu" (silu(g) u) or "clamped_swish"
+    (g' sigmoid(alpha g') (u' + 1) with g' = min(g, limit), u' = clamp(u, -limit, limit))."""
 
-    def __init__(self, weights: dict, dtype, device):
+    KINDS = {"gelu_tanh": ops.GLU_GELU_TANH, "silu": ops.GLU_SILU, "clamped_swish": ops.GLU_CLAMPED_SWISH}
+
+    def __init__(self, weights: dict, dtype, device, act: str = "gelu_tanh", limit: float = 0.0, alpha: float = 1.0):
         d = lambda t: t.to(device=device, dtype=dtype).contiguous()
         self.w_gu, self.w_down, self.dtype = d(torch.cat([weights["gate"], weights["up"]], 0)), d(weights["down"]), dtype
+        self.kind, self.limit, self.alpha = self.KINDS[act], float(limit), float(alpha)
 
     def forward(self, h: torch.Tensor) -> torch.Tensor:
-        return lin(ops.act_mul(lin(h, self.w_gu, self.dtype), self.dtype), self.w_down, torch.float32)
+        gu = lin(h, self.w_gu, self.dtype)
+        a = ops.act_mul(gu, self.dtype) if self.kind == ops.GLU_GELU_TANH else ops.glu(gu, self.dtype, self.kind, self.limit, self.alpha)
+        return lin(a, self.w_down, torch.float32)
+
+
+def rotary_table(dims: int, base: float, factor: float = 1.0) -> torch.Tensor:
+    """Angular frequency of each rotated pair (fp64): base^(-2i / dims) / factor (linear position scaling)."""
+    i = torch.arange(dims // 2, dtype=torch.float64)
+    return torch.pow(torch.tensor(float(base), dtype=torch.float64), -2.0 * i / dims) / float(factor)
+
+
+class MultiMapAttention:
+    """weights: q [H M d, W], k [G M d, W], v [G dv, W] (each with an optional bias `<name>_b`), q_norm / k_norm [d] (optional RMS norm
+    weights, shared by heads and maps), g [H, W] (optional output gate), o [W, H dv].  Rows of q and k are laid out head by head as
+    [map 0, map 1, ...].  own_kv False: no k / v tensors, the layer reads the cache pools it is given.
+
+    A head's output is sum_m map_coef[m] * softmax(q_m k_m^T scale) v over the visible keys (same chunk of `chunk` positions counted
+    from position 0, at most `window` back, causal); with unit_norm it is divided by its root mean square and multiplied by
+    post_scale; with a gate it is multiplied by sigmoid(g h)."""
+
+    def __init__(self, weights: dict, heads: int, kv_heads: int, maps: int, dim: int, vdim: int, scale: float, eps: float, dtype, device,
+                 chunk=None, window=None, rot_dims: int = 0, rot_base: float = 10000.0, rot_factor: float = 1.0, map_coef=None,
+                 unit_norm: bool = False, post_scale: float = 1.0, own_kv: bool = True):
+        if heads % kv_heads:
+            raise ValueError("heads must be a multiple of kv_heads")
+        if rot_dims > dim or rot_dims % 2:
+            raise ValueError("rotated dimensions must be even and at most dim")
+        self.H, self.G, self.M, self.d, self.dv = heads, kv_heads, int(maps), dim, vdim
+        self.scale, self.eps, self.dtype, self.device, self.own_kv = float(scale), float(eps), dtype, device, bool(own_kv)
+        self.chunk = int(chunk) if chunk else 0
+        self.window = int(window) if window else 1 << 30
+        self.rot_dims = int(rot_dims)
+        self.freq = rotary_table(self.rot_dims, rot_base, rot_factor).to(device) if self.rot_dims else None
+        self.unit_norm, self.post_scale = bool(unit_norm), float(post_scale)
+        d = lambda t: t.to(device=device, dtype=dtype).contiguous()
+        f = lambda t: t.to(device=device, dtype=torch.float32).contiguous()
+        self.map_coef = f(torch.as_tensor(map_coef, dtype=torch.float64)) if map_coef is not None else None
+        if self.map_coef is not None and self.map_coef.numel() != self.M:
+            raise ValueError("one coefficient per map")
+        names = ["q"] + (["k", "v"] if own_kv else [])
+        rows = [weights[n] for n in names]
+        self.gate_off = sum(r.shape[0] for r in rows) if "g" in weights else -1
+        if "g" in weights:
+            rows.append(weights["g"])
+        self.w_in = d(torch.cat(rows, 0))                                   # one projection: [q | k | v | gate]
+        if any(n + "_b" in weights for n in names):
+            self.bias = f(torch.cat([weights.get(n + "_b", torch.zeros(weights[n].shape[0])).float() for n in names], 0))
+        else:
+            self.bias = None
+        self.q_norm = f(weights["q_norm"]) if "q_norm" in weights else None
+        self.k_norm = f(weights["k_norm"]) if (own_kv and "k_norm" in weights) else None
+        self.w_o = d(weights["o"])
+
+    def cache_dims(self):
+        return self.G * self.M * self.d, self.G * self.dv
+
+    def forward(self, h: torch.Tensor, tb: ops.StepTables, kc: torch.Tensor, vc: torch.Tensor, page_size: int) -> torch.Tensor:
+        lib, T, H, G, M = ops.load(), h.shape[0], self.H, self.G, self.M
+        proj = lin(h, self.w_in, torch.float32)
+        ldp = proj.stride(0)
+        s = torch.cuda.current_stream(h.device).cuda_stream
+        dtc = ops.dt_code(kc.dtype)
+        ops.check(lib.kb2_seq_head_kv_prep(proj.data_ptr(), ldp, T, H, G if self.own_kv else 0, M, self.d, self.dv, ops._ptr(self.bias),
+                                           ops._ptr(self.q_norm), ops._ptr(self.k_norm), self.eps, ops._ptr(self.freq), self.rot_dims,
+                                           tb.positions.data_ptr(), tb.seq_of.data_ptr(), tb.pages.data_ptr(), tb.max_pages, page_size,
+                                           kc.data_ptr(), vc.data_ptr(), dtc, s))
+        # a step of few tokens (decoding) cuts each token's keys into pieces so that the whole GPU works on them
+        reach = min(self.window, self.chunk) if self.chunk else self.window
+        max_keys = max(min(reach, start + n) for _, n, start, _ in tb.layout)
+        nsplit = max(1, min(296 // max(T * G, 1), (max_keys + 31) // 32, 64))
+        a = part_acc = part_ml = None
+        if nsplit > 1:
+            part_acc = torch.empty((T * H * M, nsplit, self.dv), dtype=torch.float32, device=h.device)
+            part_ml = torch.empty((T * H * M, nsplit, 2), dtype=torch.float32, device=h.device)
+            a = part_acc                                                     # unused by the kernels when the range is cut
+        else:
+            a = torch.empty((T, H, M, self.dv), dtype=torch.float32, device=h.device)
+        ops.check(lib.kb2_seq_paged_attn(proj.data_ptr(), ldp, T, H, G, M, self.d, self.dv, kc.data_ptr(), vc.data_ptr(), dtc,
+                                         tb.positions.data_ptr(), tb.seq_of.data_ptr(), tb.pages.data_ptr(), tb.max_pages, page_size,
+                                         self.scale, self.chunk, min(self.window, 1 << 30), a.data_ptr(), nsplit, ops._ptr(part_acc),
+                                         ops._ptr(part_ml), None, 0, s))
+        o = torch.empty((T, H * self.dv), dtype=self.dtype, device=h.device)
+        gate = proj[:, self.gate_off:] if self.gate_off >= 0 else None
+        ops.check(lib.kb2_seq_attn_finish(a.data_ptr(), ops._ptr(part_acc), ops._ptr(part_ml), nsplit, T, H, M, self.dv, ops._ptr(self.map_coef),
+                                          int(self.unit_norm), self.eps, self.post_scale, ops._ptr(gate), ldp, o.data_ptr(),
+                                          ops.dt_code(self.dtype), None, None, 0, s))
+        return lin(o, self.w_o, torch.float32)
+
+
+class RoutedExperts:
+    """weights: router [E + identity, W], correction [E + identity] (optional), e<i>_gate / e<i>_up [F, W], e<i>_down [W, F] for i < E,
+    shared_gate / shared_up / shared_down (optional shared expert of the same SiLU form, run for every token and added).
+
+    Scores are softmax (or sigmoid) of the fp32 router logits over all E + identity outputs; the choice adds `correction`; the outputs
+    form `groups` equal groups of neighbours of which the `keep` with the largest maximal choice stay eligible; the `top` largest
+    choices are taken and weighted by their scores (renormalised if `renorm`).  The last `identity` outputs are identity experts:
+    they return their input."""
+
+    def __init__(self, weights: dict, experts: int, identity: int, top: int, dtype, device, groups: int = 1, keep: int = 1,
+                 score: str = "softmax", renorm: bool = False, out_scale: float = 1.0):
+        d = lambda t: t.to(device=device, dtype=dtype).contiguous()
+        self.E, self.ident, self.top, self.groups, self.keep = int(experts), int(identity), int(top), int(groups), int(keep)
+        self.score, self.renorm, self.out_scale, self.dtype, self.device = score, bool(renorm), float(out_scale), dtype, device
+        if weights["router"].shape[0] != self.E + self.ident:
+            raise ValueError("router rows must equal experts + identity experts")
+        if (self.E + self.ident) % self.groups or not 1 <= self.keep <= self.groups:
+            raise ValueError("expert groups must divide experts + identity experts, 1 <= keep <= groups")
+        self.w_router = d(weights["router"])
+        self.correction = weights["correction"].to(device=device, dtype=torch.float32).contiguous() if "correction" in weights else None
+        if self.E:
+            self.w_gu = d(torch.stack([torch.cat([weights[f"e{i}_gate"], weights[f"e{i}_up"]], 0) for i in range(self.E)], 0))   # [E, 2F, W]
+            self.w_down = d(torch.stack([weights[f"e{i}_down"] for i in range(self.E)], 0))                                      # [E, W, F]
+            self.F = self.w_down.shape[2]
+        self.shared = GatedMLP({k[len("shared_"):]: v for k, v in weights.items() if k.startswith("shared_")}, dtype, device, act="silu") \
+            if "shared_gate" in weights else None
+        self.tile = ops.load().kb2_seq_moe_tile_rows()
+        self.gemv_max_tokens = 8
+
+    def route(self, h: torch.Tensor):
+        return ops.route(lin(h, self.w_router, torch.float32), self.correction, self.top, self.groups, self.keep, self.score, self.renorm,
+                         self.out_scale)
+
+    def forward(self, h: torch.Tensor) -> torch.Tensor:
+        lib, T, W, E, top = ops.load(), h.shape[0], h.shape[1], self.E, self.top
+        dev, s = h.device, torch.cuda.current_stream(h.device).cuda_stream
+        ids, wts = self.route(h)
+        dt, dtc = self.dtype, ops.dt_code(self.dtype)
+        slots = T * top
+        y = pos = None
+        if E and T <= self.gemv_max_tokens:
+            F2 = self.w_gu.shape[1]
+            gu = torch.zeros((slots, F2), dtype=dt, device=dev)
+            ops.check(lib.kb2_seq_moe_gemv(h.data_ptr(), ops.dt_code(h.dtype), h.stride(0), top, ids.data_ptr(), E, self.w_gu.data_ptr(), dtc, W,
+                                           F2 * W, gu.data_ptr(), dtc, F2, slots, F2, W, s))
+            act = ops.glu(gu, dt, ops.GLU_SILU)
+            y = torch.empty((slots, W), dtype=torch.float32, device=dev)
+            ops.check(lib.kb2_seq_moe_gemv(act.data_ptr(), dtc, self.F, 1, ids.data_ptr(), E, self.w_down.data_ptr(), dtc, self.F, W * self.F,
+                                           y.data_ptr(), 0, W, slots, W, self.F, s))
+        elif E:
+            F2, tile = self.w_gu.shape[1], self.tile
+            max_rows = (slots + E * (tile - 1) + tile - 1) // tile * tile
+            max_tiles = max_rows // tile
+            ints = torch.empty(3 * E + 2 + max_tiles + max_rows + slots, dtype=torch.int32, device=dev)
+            counts, offs, cursor = ints[:E], ints[E:2 * E + 1], ints[2 * E + 1:3 * E + 1]
+            n_tiles = ints[3 * E + 1:3 * E + 2]
+            tile_expert = ints[3 * E + 2:3 * E + 2 + max_tiles]
+            slot_row = ints[3 * E + 2 + max_tiles:3 * E + 2 + max_tiles + max_rows]
+            pos = ints[3 * E + 2 + max_tiles + max_rows:]
+            ops.check(lib.kb2_seq_moe_bin(ids.data_ptr(), slots, E, counts.data_ptr(), offs.data_ptr(), cursor.data_ptr(), tile_expert.data_ptr(),
+                                          n_tiles.data_ptr(), slot_row.data_ptr(), max_rows, pos.data_ptr(), s))
+            gu = torch.empty((max_rows, F2), dtype=dt, device=dev)
+            ops.check(lib.kb2_seq_moe_gemm(h.data_ptr(), ops.dt_code(h.dtype), h.stride(0), slot_row.data_ptr(), top, self.w_gu.data_ptr(), dtc, W,
+                                           F2 * W, gu.data_ptr(), dtc, F2, F2, W, tile_expert.data_ptr(), n_tiles.data_ptr(), max_tiles, s))
+            act = ops.glu(gu, dt, ops.GLU_SILU, n_tiles=n_tiles, tile_rows=tile)
+            y = torch.empty((max_rows, W), dtype=torch.float32, device=dev)
+            ops.check(lib.kb2_seq_moe_gemm(act.data_ptr(), dtc, self.F, None, 1, self.w_down.data_ptr(), dtc, self.F, W * self.F, y.data_ptr(), 0,
+                                           W, W, self.F, tile_expert.data_ptr(), n_tiles.data_ptr(), max_tiles, s))
+        shared = self.shared.forward(h) if self.shared is not None else None
+        out = torch.empty((T, W), dtype=torch.float32, device=dev)
+        ops.check(lib.kb2_seq_moe_combine(ops._ptr(y), ops._ptr(pos), ids.data_ptr(), wts.data_ptr(), T, top, E, self.ident, h.data_ptr(),
+                                          ops.dt_code(h.dtype), ops._ptr(shared), out.data_ptr(), W, s))
+        return out
 
 
 class TokenSideInput:

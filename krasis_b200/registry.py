@@ -24,6 +24,13 @@ def _vofelix(model_dir, dtype=torch.bfloat16, device=0, **kw):
     return VofelixModel.from_pretrained(model_dir, dtype=dtype, device=device, **kw)
 
 
+def _megolorn(model_dir, dtype=torch.bfloat16, device=0, **kw):
+    from .build import build_seq
+    build_seq()
+    from .megolorn import MegolornModel
+    return MegolornModel.from_pretrained(model_dir, dtype=dtype, device=device, **kw)
+
+
 def _hf_moe(model_dir, dtype=torch.bfloat16, device=0, **kw):
     if dtype != torch.bfloat16:
         raise ValueError("the MoE prefill models run in bfloat16 only")
@@ -34,6 +41,7 @@ def _hf_moe(model_dir, dtype=torch.bfloat16, device=0, **kw):
 
 
 register("Vofelix", _vofelix)
+register("Megolorn", _megolorn)
 for _name in _HF_MOE:
     register(_name, _hf_moe)
 

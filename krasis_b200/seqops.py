@@ -25,6 +25,17 @@ SIGNATURES = {
     "kb2_seq_latent_window_attn": (_I, [_P, _P, _L, _I, _I, _I, _I, _I, _P, _P, _I, _P, _P, _P, _I, _I, _P, _F, _I, _P, _P, _I, _I, _P, _P, _P]),
     "kb2_seq_conv_silu": (_I, [_P, _L, _I, _I, _I, _I, _P, _P, _P, _P, _P, _P, _P]),
     "kb2_seq_delta_rule": (_I, [_P, _I, _P, _L, _I, _I, _I, _I, _I, _I, _I, _I, _I, _P, _P, _P, _F, _P, _P, _P, _P, _P, _I, _P]),
+    "kb2_seq_residual_add_norm": (_I, [_P, _P, _P, _P, _P, _P, _I, _I, _I, _F, _P]),
+    "kb2_seq_head_kv_prep": (_I, [_P, _L, _I, _I, _I, _I, _I, _I, _P, _P, _P, _F, _P, _I, _P, _P, _P, _I, _I, _P, _P, _I, _P]),
+    "kb2_seq_paged_attn": (_I, [_P, _L, _I, _I, _I, _I, _I, _I, _P, _P, _I, _P, _P, _P, _I, _I, _F, _I, _I, _P, _I, _P, _P, _P, _I, _P]),
+    "kb2_seq_attn_finish": (_I, [_P, _P, _P, _I, _I, _I, _I, _I, _P, _I, _F, _F, _P, _L, _P, _I, _P, _P, _I, _P]),
+    "kb2_seq_glu": (_I, [_P, _I, _L, _P, _I, _L, _I, _I, _F, _F, _P, _I, _P]),
+    "kb2_seq_route": (_I, [_P, _L, _I, _I, _P, _I, _I, _I, _I, _I, _F, _P, _P, _P]),
+    "kb2_seq_moe_tile_rows": (_I, []),
+    "kb2_seq_moe_bin": (_I, [_P, _L, _I, _P, _P, _P, _P, _P, _P, _L, _P, _P]),
+    "kb2_seq_moe_gemm": (_I, [_P, _I, _L, _P, _I, _P, _I, _L, _L, _P, _I, _L, _I, _I, _P, _P, _I, _P]),
+    "kb2_seq_moe_gemv": (_I, [_P, _I, _L, _I, _P, _I, _P, _I, _L, _L, _P, _I, _L, _I, _I, _I, _P]),
+    "kb2_seq_moe_combine": (_I, [_P, _P, _P, _P, _I, _I, _I, _I, _P, _I, _P, _P, _I, _P]),
 }
 
 _lib = None
@@ -210,3 +221,41 @@ def side_gate(g: torch.Tensor, table: torch.Tensor, tokens: torch.Tensor, col0: 
     check(load().kb2_seq_side_gate(g.data_ptr(), table.data_ptr(), dt_code(table.dtype), table.stride(0), tokens.data_ptr(), col0, dim, T,
                                    out.data_ptr(), dt_code(out_dtype), _s(g)))
     return out
+
+
+def residual_add_norm(x, y=None, y2=None, out_norm=None, out_dtype=torch.float32, eps=1e-5):
+    """x (fp32, in place) += (y + y2); returns layer_norm(x) with out_norm = (weight, bias or None), or None."""
+    T, W = x.shape
+    for t in (y, y2):
+        if t is not None and (t.dtype != torch.float32 or not t.is_contiguous() or t.shape != x.shape):
+            raise ValueError("residual_add_norm: addends must be contiguous fp32 of x's shape")
+    h = torch.empty((T, W), dtype=out_dtype, device=x.device) if out_norm is not None else None
+    wb, bb = out_norm if out_norm is not None else (None, None)
+    check(load().kb2_seq_residual_add_norm(x.data_ptr(), _ptr(y), _ptr(y2), _ptr(wb), _ptr(bb), _ptr(h), dt_code(out_dtype), T, W, float(eps),
+                                           _s(x)))
+    return h
+
+
+GLU_GELU_TANH, GLU_SILU, GLU_CLAMPED_SWISH = 0, 1, 2
+
+
+def glu(gate_up: torch.Tensor, out_dtype, kind: int, limit: float = 0.0, alpha: float = 1.0, n_tiles=None, tile_rows: int = 0) -> torch.Tensor:
+    """[rows, 2F] = [gate | up] -> [rows, F]; see kb2_seq_glu for the kinds."""
+    rows, F2 = gate_up.shape
+    out = torch.empty((rows, F2 // 2), dtype=out_dtype, device=gate_up.device)
+    check(load().kb2_seq_glu(gate_up.data_ptr(), dt_code(gate_up.dtype), gate_up.stride(0), out.data_ptr(), dt_code(out_dtype), rows, F2 // 2,
+                             int(kind), float(limit), float(alpha), _ptr(n_tiles), int(tile_rows), _s(gate_up)))
+    return out
+
+
+def route(z: torch.Tensor, correction, top: int, groups: int = 1, keep: int = 1, score: str = "softmax", renorm: bool = False,
+          out_scale: float = 1.0):
+    """Router logits z [T, E] fp32 -> (ids [T, top] int32, weights [T, top] fp32)."""
+    if z.dtype != torch.float32 or z.stride(1) != 1:
+        raise ValueError("route: logits must be fp32 rows")
+    T, E = z.shape
+    ids = torch.empty((T, top), dtype=torch.int32, device=z.device)
+    w = torch.empty((T, top), dtype=torch.float32, device=z.device)
+    check(load().kb2_seq_route(z.data_ptr(), z.stride(0), T, E, _ptr(correction), {"softmax": 0, "sigmoid": 1}[score], int(groups), int(keep),
+                               int(top), int(renorm), float(out_scale), ids.data_ptr(), w.data_ptr(), _s(z)))
+    return ids, w

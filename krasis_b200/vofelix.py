@@ -151,14 +151,7 @@ class VofelixModel:
         from . import loader
         raw = json.load(open(os.path.join(model_dir, "config.json")))
         cfg = VofelixConfig.from_dict(raw)
-        files = loader.open_model_safetensors(model_dir)
-        weights = {}
-        for name, f in files.items():
-            kind = f.header[name]["dtype"]
-            if kind in ("BF16", "F32", "F16"):
-                weights[name] = loader._st_bf16(files, name).float() if kind == "BF16" else torch.from_numpy(f.tensor(name).copy()).float()
-            else:                                   # integer tables are kept as they are
-                weights[name] = torch.from_numpy(f.tensor(name).copy())
+        weights = loader.read_named_tensors(model_dir)
         return cls(cfg, weights, dtype=dtype, device=device)
 
     @classmethod
