@@ -355,6 +355,14 @@ KB2_API int kb2_fmha_latent(const void* q_dev, const void* kv_up_dev, const void
                             int32_t kv_len, int32_t num_heads, float sm_scale, int32_t window, const float* sinks_dev, int32_t device,
                             void* stream);
 
+/* Attention core on dense BF16 rows for heads that carry several attention maps (keys per map, shared values): q [M][num_q * 128] with
+ * num_q = heads * maps query vectors laid out head by head, map by map; k [kv_len][num_kv_heads * maps * 128]; v [kv_len][num_kv_heads *
+ * v_dim], v_dim 128 or 256; out [M][num_q * v_dim] fp32 (one softmax-weighted value row per query vector; combining the maps is the
+ * caller's).  Query i stands at position q_start + i of the kv rows and sees the keys with 0 <= position - key < window. */
+KB2_API int kb2_fmha_maps(const void* q_dev, const void* k_dev, const void* v_dev, float* out_dev, int32_t M, int32_t q_start,
+                          int32_t kv_len, int32_t num_q, int32_t num_kv_heads, int32_t maps, int32_t v_dim, float sm_scale, int32_t window,
+                          int32_t device, void* stream);
+
 /* GEMM -> reduce-scatter fused (head-parallel attention under token sharding): after kb2_{gdn,gqa,mla}_set_output_scatter the
  * block's out_proj GEMM stores every output row straight into the receive buffer of the rank that owns the token
  * (peer_recv_host[r] from kb2_comm_peer_alloc, layout [M / num_ranks][num_ranks][hidden] bf16, slot = src_rank) instead of out_dev

@@ -1,4 +1,4 @@
-"""Throughput of a ragged-batch model (Vofelix) at layer sizes of real models, beside the framework's closest existing blocks at
+"""Throughput of the ragged-batch models (Vofelix, Megolorn) at layer sizes of real models, beside the framework's closest existing blocks at
 equal size: prefill tokens/s (one prompt, whole and in portions), decode tokens/s (several live requests, one token each per step),
 and per-mixer times — the gated delta mixer against the Gated-DeltaNet block, windowed latent attention against the MLA block.
 Random weights; device timing with CUDA events after warm-up; the weights of a step exceed the L2 cache."""
@@ -136,5 +136,126 @@ def run(args, peaks):
     except Exception as exc:       # noqa: BLE001 — the comparison is optional; the new design's numbers stand without it
         mix["comparison_unavailable"] = f"{type(exc).__name__}: {exc}"
     out["mixers_at_equal_size"] = mix
+    out["peaks"] = peaks
+    print(json.dumps(out))
+
+
+# ------------------------------------------------------------------------------------------------ Megolorn
+def megolorn_config(width=2048, chunk=2048, vocab=32768, experts=62, identity=2, top=6, expert_ff=1024):
+    """16 query heads x 2 maps x 128 over 2 key/value heads with 256-wide values: the score and value products of the GQA block of
+    Qwen3-Next (16 heads x 256 over 2 key/value heads) with the value product doubled.  Every other layer reads the previous layer's
+    keys and values and carries routed experts (64 router outputs in 8 groups, 4 kept, top 6) with a shared expert."""
+    att = {"heads": 16, "kv_heads": 2, "dim": 128, "vdim": 256, "diff": 0.6, "scale": 128 ** -0.5, "mask": {"size": chunk},
+           "rot": {"base": 1000000.0, "dims": 64, "scaling": {"factor": 8.0}}}
+    moe = {"kind": "moe", "expert": {"ff": expert_ff}, "shared": {"ff": 2 * expert_ff},
+           "router": {"experts": experts, "identity": identity, "top": top, "groups": {"count": 8, "keep": 4}}}
+    dense = {"kind": "dense", "ff": 4 * width, "limit": 7.0}
+    layers = []
+    for i in range(2):
+        layers.append({"type": "attention", "mixer": dict(att), "mlp": dense})
+        layers.append({"type": "attention", "mixer": dict(att, kv_from=2 * i), "mlp": moe})
+    return {"architecture": "Megolorn", "vocab": vocab, "width": width, "embedding": {"scale": 8.0}, "norm": {"eps": 1e-6}, "layers": layers}
+
+
+def run_megolorn(args, peaks):
+    from . import seqops as ops
+    from .build import build, build_seq
+    build_seq()
+    build()                                          # the tcgen05 GEMM and attention core serve long bfloat16 steps
+    from .megolorn import MegolornConfig, MegolornModel
+    from .scheduler import Scheduler
+    dev = torch.device("cuda", 0)
+    tokens = args.tokens or 4096
+    raw = megolorn_config()
+    cfg = MegolornConfig.from_dict(raw)
+    model = MegolornModel.random(cfg, seed=0, dtype=torch.bfloat16, device=0)
+    g = torch.Generator().manual_seed(0)
+    prompt = torch.randint(0, cfg.vocab, (tokens,), generator=g).tolist()
+    out = {"metric": "megolorn_prefill_tokens_per_s", "unit": "tokens/s", "n_gpus": 1, "steps": args.steps, "warmup": args.warmup,
+           "higher_is_better": True, "dtype": "bf16", "data": "synthetic (random weights and token ids)", "vs_baseline": None,
+           "config": {"model": "megolorn width 2048: 4 layers, differential attention 16 heads x 2 maps x 128 / 2 kv heads / values 256, "
+                               "chunk 2048; layers 1 and 3 read the keys and values of layers 0 and 2; dense ff 8192 / 62 experts + 2 identity, "
+                               "top 6, expert ff 1024, shared ff 2048", "prompt_tokens": tokens,
+                      "l2": "weights of one step (about 1.8 GB) exceed L2"}}
+    launches0 = ops.total_launches()
+
+    def prefill(portion):
+        s = Scheduler(model, max_tokens=tokens + 64, max_requests=4)
+        at = 0
+        while at < tokens:
+            n = min(portion, tokens - at)
+            lg = s.step([("p", prompt[at:at + n], [n - 1] if at + n == tokens else [])])
+            at += n
+        s.finish("p")
+        return lg
+    ms = _time(lambda: prefill(tokens), args.warmup, args.steps)
+    out.update(value=round(tokens / ms * 1e3, 1), ms_per_step=round(ms, 3))
+    ms_p = _time(lambda: prefill(512), 1, max(1, args.steps // 2))
+    out["prefill_portions_512"] = {"tokens_per_s": round(tokens / ms_p * 1e3, 1), "ms": round(ms_p, 3)}
+
+    ctx = 2048
+    s = Scheduler(model, max_tokens=4 * (ctx + 256), max_requests=4, cuda_graphs=not getattr(args, 'no_graph', False))
+    for r in range(4):
+        s.step([(r, prompt[:ctx], [])])
+    nxt = [[1], [2], [3], [4]]
+    ms_d = _time(lambda: s.step([(r, nxt[r], [0]) for r in range(4)]), args.warmup, 16)
+    out["decode"] = {"live_requests": 4, "context": ctx, "tokens_per_s": round(4 / ms_d * 1e3, 1), "ms_per_step": round(ms_d, 3),
+                     "cuda_graph": bool(s.cuda_graphs and any(v not in (None, False) for v in s._graphs.values()))}
+    out["gpu_launches"] = ops.total_launches() - launches0
+
+    s = Scheduler(model, max_tokens=tokens + 256, max_requests=4)
+    s.generate([prompt], max_new_tokens=8, step_tokens=tokens)
+    t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    torch.cuda.synchronize()
+    h2d0, steps0 = s.h2d_bytes, s.steps_run
+    t0.record()
+    s.generate([prompt], max_new_tokens=8, step_tokens=tokens)
+    t1.record()
+    torch.cuda.synchronize()
+    out["e2e"] = {"value": round((tokens + 8) / t0.elapsed_time(t1) * 1e3, 1), "unit": "tokens/s (prompt + 8 generated, Scheduler.generate)",
+                  "h2d_bytes_per_step": (s.h2d_bytes - h2d0) // max(s.steps_run - steps0, 1), "d2h_bytes_per_step": 8}
+
+    # ---- per-block times, prefill and decode, beside the closest blocks at equal size
+    blk = {}
+    W = cfg.width
+    h = (torch.randn(tokens, W, generator=g) * 0.5).to(torch.bfloat16).to(dev)
+    tb = ops.StepTables([(prompt, 0, 0, list(range((tokens + 63) // 64)))], dev)
+    model.make_caches(tokens + 64, 4)
+    att = model.layers[0]["mixer"]
+    kc, vc = model.kv_cache.get_layer_caches(0)
+    blk["differential_attention_block_ms"] = round(_time(lambda: att.forward(h, tb, kc, vc, 64), 2, 5), 3)
+    att.tc_min_portion = 1 << 30
+    hs = h[:512].contiguous()
+    tbs = ops.StepTables([(prompt[:512], 0, 0, list(range(8)))], dev)
+    blk["differential_attention_block_plain_kernel_512_tokens_ms"] = round(_time(lambda: att.forward(hs, tbs, kc, vc, 64), 1, 3), 3)
+    att.tc_min_portion = 128
+    blk["dense_ff_8192_ms"] = round(_time(lambda: model.layers[0]["mlp"].forward(h), 2, 5), 3)
+    moe = model.layers[1]["mlp"]
+    blk["routed_experts_block_ms"] = round(_time(lambda: moe.forward(h), 2, 5), 3)
+    h4 = h[:4].contiguous()
+    tb4 = ops.StepTables([([1], ctx, r, list(range(r * 40, r * 40 + 33))) for r in range(4)], dev)
+    blk["decode_4_tokens_attention_ms"] = round(_time(lambda: att.forward(h4, tb4, kc, vc, 64), 3, 20), 4)
+    blk["decode_4_tokens_routed_experts_ms"] = round(_time(lambda: moe.forward(h4), 3, 20), 4)
+    blk["decode_4_tokens_dense_ff_ms"] = round(_time(lambda: model.layers[0]["mlp"].forward(h4), 3, 20), 4)
+    try:
+        from types import SimpleNamespace
+        from .attention import GQAAttention, PagedKVCache, SequenceKVState
+        from .model import HybridMoEConfig, SyntheticWeights
+        hc = HybridMoEConfig(hidden_size=W, num_attention_heads=16, num_key_value_heads=2, gqa_head_dim=256, rope_theta=1000000.0,
+                             rms_norm_eps=1e-6)
+        src = SyntheticWeights(hc, dev, 0)
+        ac = SimpleNamespace(**{f: getattr(hc, f) for f in hc.__dataclass_fields__})
+        gqa = GQAAttention(ac, 0, src.attention(0, "full_attention"), dev, max_tokens=tokens)
+        kv = PagedKVCache.from_config(ac, 1, dev, max_pages=tokens // 16 + 2)
+        pos = torch.arange(tokens, dtype=torch.int32, device=dev)
+
+        def gqa_step():
+            st = SequenceKVState(kv)
+            gqa.forward(h, pos, kv, st, 0, num_new_tokens=tokens)
+            st.free()
+        blk["gqa_block_16x256_full_causal_ms"] = round(_time(gqa_step, 2, 5), 3)
+    except Exception as exc:       # noqa: BLE001 — the comparison is optional; the new design's numbers stand without it
+        blk["comparison_unavailable"] = f"{type(exc).__name__}: {exc}"
+    out["blocks_at_equal_size"] = blk
     out["peaks"] = peaks
     print(json.dumps(out))

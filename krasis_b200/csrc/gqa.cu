@@ -180,7 +180,10 @@ __global__ void __launch_bounds__(kFThreads, 1)
                     __nv_bfloat16* __restrict__ out,             // [M][nh*DV]
                     int M, int q_start, int kv_len, float sm_scale_log2, int k_col0, int v_col0,
                     int window = 1 << 30,                        // a query sees the keys with 0 <= q_pos - key < window
-                    const float* __restrict__ sinks = nullptr) { // per head: exp(sink) joins the softmax denominator (no value)
+                    const float* __restrict__ sinks = nullptr,   // per head: exp(sink) joins the softmax denominator (no value)
+                    int maps = 1,                                // query heads come in groups of `maps` attention maps: map m of a head reads
+                                                                 // key head kvh * maps + m, every map reads value head kvh
+                    float* __restrict__ out_f32 = nullptr) {     // if given, the output rows are written here in fp32 (no gate), not to `out`
   using L = FmhaSmem<DQ, DV>;
   constexpr int D = DQ;
   constexpr int NC = DQ / 64;                      // 64-wide d chunks of q/k
@@ -201,7 +204,7 @@ __global__ void __launch_bounds__(kFThreads, 1)
   // from a divergent `lane == 0` branch each tcgen05.mma pays an ELECT + R2UR.BROADCAST loop of ~50 cycles, more than an N=64 MMA runs)
   const int warp = __shfl_sync(0xffffffffu, (int)(threadIdx.x >> 5), 0), lane = threadIdx.x & 31;
   const int qt = gridDim.x - 1 - blockIdx.x;       // heavy (late) query tiles first
-  const int head = blockIdx.y, kvh = head / (g.nh / g.nkv);
+  const int head = blockIdx.y, kvh = (head / maps) / ((g.nh / maps) / g.nkv), kkh = kvh * maps + head % maps;
   const int q0 = qt * kFQ;
   // keys visible to this tile: positions <= q_start + min(q0 + 127, M - 1)
   const int last_q = min(q0 + kFQ - 1, M - 1);
@@ -237,7 +240,7 @@ __global__ void __launch_bounds__(kFThreads, 1)
   if (warp < 4) {
     // ------------------------------------------------------------ KV producer: one thread issues the TMA boxes of a tile
     if (warp == 0) {
-      const int kx = k_col0 + kvh * (PE ? DQ - 64 : DQ), vx = v_col0 + kvh * DV;
+      const int kx = k_col0 + kkh * (PE ? DQ - 64 : DQ), vx = v_col0 + kvh * DV;
       int stage = 0;
       uint32_t phase = 0;
       for (int it = 0; it < n_tiles; ++it) {
@@ -456,7 +459,13 @@ __global__ void __launch_bounds__(kFThreads, 1)
         uint32_t r[16];
         tmem_ld16(lane_addr + kColO + c0, r);
         tmem_ld_wait();
-        if (live) {
+        if (live && out_f32 != nullptr) {
+          float4* dst = reinterpret_cast<float4*>(out_f32 + obase + c0);
+#pragma unroll
+          for (int jj = 0; jj < 16; jj += 4)
+            dst[jj / 4] = make_float4(__uint_as_float(r[jj]) * inv_l, __uint_as_float(r[jj + 1]) * inv_l, __uint_as_float(r[jj + 2]) * inv_l,
+                                      __uint_as_float(r[jj + 3]) * inv_l);
+        } else if (live) {
           uint32_t o[8];
           uint4 gq[2] = {make_uint4(0, 0, 0, 0), make_uint4(0, 0, 0, 0)};
           if (gated) {
@@ -731,6 +740,42 @@ cudaError_t launch_fmha_latent(const void* q, const void* kv_up, const void* kpe
   KernelSpan ks(K_FMHA, s);
   gqa_fmha_kernel<192, 128, true><<<grid, kFThreads, FmhaSmem<192, 128>::kTotal, s>>>(
       tq, tk, tpe, tk, g, nullptr, (__nv_bfloat16*)out, M, q_start, kv_len, sm_scale * 1.4426950408889634f, 0, nh * 128, window, sinks);
+  return cudaGetLastError();
+}
+
+// Attention core on dense BF16 rows for heads that carry several attention maps: q [M][nq * 128] with nq = heads * maps query
+// vectors (head by head, map by map), k [kv_len][nkv * maps * 128], v [kv_len][nkv * dv], dv 128 or 256; out_f32 [M][nq * dv] fp32.
+// Query i stands at position q_start + i of the kv rows and sees the keys with 0 <= position - key < window.
+cudaError_t launch_fmha_maps(const void* q, const void* k, const void* v, float* out_f32, int M, int q_start, int kv_len, int nq, int nkv,
+                             int maps, int dv, float sm_scale, int window, cudaStream_t s) {
+  if (M <= 0 || nq <= 0 || nkv <= 0 || maps <= 0 || nq % maps || (nq / maps) % nkv || q_start < 0 || kv_len != q_start + M || window <= 0 ||
+      (dv != 128 && dv != 256))
+    return cudaErrorInvalidValue;
+  static PerDeviceOnce once;
+  if (const int dev = once.pending(); dev >= 0) {
+    cudaError_t e0 = cudaFuncSetAttribute(gqa_fmha_kernel<128, 128, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, FmhaSmem<128, 128>::kTotal);
+    if (e0 != cudaSuccess) return e0;
+    e0 = cudaFuncSetAttribute(gqa_fmha_kernel<128, 256, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, FmhaSmem<128, 256>::kTotal);
+    if (e0 != cudaSuccess) return e0;
+    once.mark(dev);
+  }
+  alignas(64) CUtensorMap tq, tk, tv;
+  cudaError_t e = make_tmap_bf16_rows(&tq, q, M, (long long)nq * 128, kFQ);
+  if (e != cudaSuccess) return e;
+  e = make_tmap_bf16_rows(&tk, k, kv_len, (long long)nkv * maps * 128, kFK);
+  if (e != cudaSuccess) return e;
+  e = make_tmap_bf16_rows(&tv, v, kv_len, (long long)nkv * dv, kFK);
+  if (e != cudaSuccess) return e;
+  GqaDims g{0, nq, nkv, 128, 0, 0, 0.f, 0.f};
+  dim3 grid((M + kFQ - 1) / kFQ, nq);
+  KernelSpan ks(K_FMHA, s);
+  const float sl2 = sm_scale * 1.4426950408889634f;
+  if (dv == 256)
+    gqa_fmha_kernel<128, 256, false><<<grid, kFThreads, FmhaSmem<128, 256>::kTotal, s>>>(tq, tk, tk, tv, g, nullptr, nullptr, M, q_start, kv_len,
+                                                                                          sl2, 0, 0, window, nullptr, maps, out_f32);
+  else
+    gqa_fmha_kernel<128, 128, false><<<grid, kFThreads, FmhaSmem<128, 128>::kTotal, s>>>(tq, tk, tk, tv, g, nullptr, nullptr, M, q_start, kv_len,
+                                                                                          sl2, 0, 0, window, nullptr, maps, out_f32);
   return cudaGetLastError();
 }
 

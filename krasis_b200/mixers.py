@@ -259,9 +259,37 @@ class MultiMapAttention:
         self.q_norm = f(weights["q_norm"]) if "q_norm" in weights else None
         self.k_norm = f(weights["k_norm"]) if (own_kv and "k_norm" in weights) else None
         self.w_o = d(weights["o"])
+        # long prompt portions in bfloat16 with 128 query / key dims per map and 128 or 256 value dims run the tcgen05 attention core of
+        # the MoE prefill models, one call per chunk the portion touches, on keys and values gathered from the pages
+        self.tc_min_portion = 128
+        self.tc_shape = dtype == torch.bfloat16 and dim == 128 and vdim in (128, 256)
 
     def cache_dims(self):
         return self.G * self.M * self.d, self.G * self.dv
+
+    def _tensor_core_portion(self, core, proj, a, tb, i, kc, vc, page_size, stream):
+        """Sequence i of the step on the tcgen05 kernel: a[rows of the portion] = per-map attention outputs (fp32)."""
+        import numpy as np
+        from . import capi
+        row0, n, start, pages = tb.layout[i]
+        H, G, M, d, dv, chunk = self.H, self.G, self.M, self.d, self.dv, self.chunk
+        first = start // chunk * chunk if chunk else 0
+        first = max(first, start - self.window + 1)
+        j = np.arange(first, start + n, dtype=np.int64)
+        rows = torch.from_numpy(np.asarray(pages, dtype=np.int64)[j // page_size] * page_size + j % page_size).to(proj.device, non_blocking=True)
+        k_rows = kc.view(-1, G * M * d).index_select(0, rows)
+        v_rows = vc.view(-1, G * dv).index_select(0, rows)
+        q = proj[row0:row0 + n, :H * M * d].to(torch.bfloat16).contiguous()
+        pos = start
+        while pos < start + n:
+            cstart = pos // chunk * chunk if chunk else 0
+            end = min(start + n, cstart + chunk) if chunk else start + n
+            lo = max(cstart, first)
+            m = end - pos
+            capi.check(core.kb2_fmha_maps(q[pos - start:].data_ptr(), k_rows[lo - first:].data_ptr(), v_rows[lo - first:].data_ptr(),
+                                          a[row0 + pos - start:].data_ptr(), m, pos - lo, end - lo, H * M, G, M, dv, self.scale,
+                                          min(self.window, 1 << 30), proj.device.index or 0, stream))
+            pos = end
 
     def forward(self, h: torch.Tensor, tb: ops.StepTables, kc: torch.Tensor, vc: torch.Tensor, page_size: int) -> torch.Tensor:
         lib, T, H, G, M = ops.load(), h.shape[0], self.H, self.G, self.M
@@ -277,6 +305,10 @@ class MultiMapAttention:
         reach = min(self.window, self.chunk) if self.chunk else self.window
         max_keys = max(min(reach, start + n) for _, n, start, _ in tb.layout)
         nsplit = max(1, min(296 // max(T * G, 1), (max_keys + 31) // 32, 64))
+        core = _core_lib() if self.tc_shape else False
+        fast = [i for i, (_, n, _, _) in enumerate(tb.layout) if n >= self.tc_min_portion] if core else []
+        if fast:
+            nsplit = 1
         a = part_acc = part_ml = None
         if nsplit > 1:
             part_acc = torch.empty((T * H * M, nsplit, self.dv), dtype=torch.float32, device=h.device)
@@ -284,10 +316,13 @@ class MultiMapAttention:
             a = part_acc                                                     # unused by the kernels when the range is cut
         else:
             a = torch.empty((T, H, M, self.dv), dtype=torch.float32, device=h.device)
-        ops.check(lib.kb2_seq_paged_attn(proj.data_ptr(), ldp, T, H, G, M, self.d, self.dv, kc.data_ptr(), vc.data_ptr(), dtc,
-                                         tb.positions.data_ptr(), tb.seq_of.data_ptr(), tb.pages.data_ptr(), tb.max_pages, page_size,
-                                         self.scale, self.chunk, min(self.window, 1 << 30), a.data_ptr(), nsplit, ops._ptr(part_acc),
-                                         ops._ptr(part_ml), None, 0, s))
+        if len(fast) < tb.S:
+            ops.check(lib.kb2_seq_paged_attn(proj.data_ptr(), ldp, T, H, G, M, self.d, self.dv, kc.data_ptr(), vc.data_ptr(), dtc,
+                                             tb.positions.data_ptr(), tb.seq_of.data_ptr(), tb.pages.data_ptr(), tb.max_pages, page_size,
+                                             self.scale, self.chunk, min(self.window, 1 << 30), a.data_ptr(), nsplit, ops._ptr(part_acc),
+                                             ops._ptr(part_ml), tb.cu.data_ptr() if fast else None, self.tc_min_portion, s))
+        for i in fast:
+            self._tensor_core_portion(core, proj, a, tb, i, kc, vc, page_size, s)
         o = torch.empty((T, H * self.dv), dtype=self.dtype, device=h.device)
         gate = proj[:, self.gate_off:] if self.gate_off >= 0 else None
         ops.check(lib.kb2_seq_attn_finish(a.data_ptr(), ops._ptr(part_acc), ops._ptr(part_ml), nsplit, T, H, M, self.dv, ops._ptr(self.map_coef),

@@ -112,6 +112,14 @@ def f64(d):
     return {k: v.numpy().astype(np.float64) for k, v in d.items()}
 
 
+def _peaky(names, factor):
+    def tweak(w):
+        for k in list(w):
+            if any(k.endswith(n) for n in names):
+                w[k] = (w[k] * factor).to(torch.bfloat16).float()
+    return tweak
+
+
 # ------------------------------------------------------------------------------------------------ mechanisms alone
 
 def attn_weights(m, W, seed, own=True):
@@ -204,6 +212,34 @@ def test_attention_decode_grid_cuts_the_key_range(seq):
     close(got, want, 3e-5, "fp32, cut key range")
     got, _ = run_mixer(seq, make_mixer(m, w, dtype=torch.bfloat16), h, [T - 3], page_size=64)
     close(got, want, 3e-2, "bf16, cut key range")
+
+
+def test_tensor_core_prefill_of_differential_attention(seq):
+    """bfloat16 with 128 query / key dims per map and 128 or 256 value dims: portions of 128 tokens or more run the tcgen05 attention
+    core, one call per chunk the portion touches.  Against the oracle and against the plain kernel on the same bf16 cache, with
+    peaked scores, chunks that end inside, at and across KV tiles, portions that start in the middle of a chunk."""
+    from krasis_b200.build import build as build_core
+    build_core()
+    for chunk, vdim, heads, kv_heads in ((100, 128, 2, 1), (64, 256, 4, 2), (333, 128, 2, 2), (None, 256, 2, 1)):
+        raw = model_cfg([L(attn_cfg(heads=heads, kv_heads=kv_heads, dim=128, vdim=vdim, chunk=chunk, rot_dims=64, scale=0.02), dense(ff=64))], width=64)
+        model, w = build(raw, dtype=torch.bfloat16, seed=31, tweak=_peaky(["q.norm", "k.norm"], 2.0))
+        mixer = model.layers[0]["mixer"]
+        assert mixer.tc_shape
+        tk = toks(700, raw["vocab"], 16)
+        want = O.forward(raw, w, tk)
+        if chunk:                                   # the chunk's edge must move the logits by far more than the tolerances below
+            wide = json.loads(json.dumps(raw))
+            wide["layers"][0]["mixer"]["mask"]["size"] = chunk + 1
+            assert np.abs(O.forward(wide, w, tk) - want).max() > 0.15 * np.abs(want).max()
+        fast_whole = run_portions(model, tk, [700], s=sched(model, 1024))
+        fast_parts = run_portions(model, tk, [130, 257, 128, 150], s=sched(model, 1024))          # then 35 single tokens through the plain kernel
+        mixer.tc_min_portion = 1 << 30
+        plain = run_portions(model, tk, [700], s=sched(model, 1024))
+        mixer.tc_min_portion = 128
+        close(plain, want, 5e-2, f"chunk {chunk}: plain kernel against the oracle")
+        close(fast_whole, want, 5e-2, f"chunk {chunk}: tensor-core prefill against the oracle")
+        close(fast_whole, plain, 3e-2, f"chunk {chunk}: tensor-core prefill against the plain kernel")
+        close(fast_parts, plain, 3e-2, f"chunk {chunk}: tensor-core portions against the plain kernel")
 
 
 def test_clamped_swish_and_silu_units(seq):
@@ -331,14 +367,6 @@ def test_pages_and_slots_are_reused(seq):
         assert s.kv_cache.free_page_count == free0 and s.state_pool.free_slot_count == 2
     with pytest.raises(RuntimeError):
         s.step([("x", toks(60, 50, 1), [])])                    # more pages than the pool has
-
-
-def _peaky(names, factor):
-    def tweak(w):
-        for k in list(w):
-            if any(k.endswith(n) for n in names):
-                w[k] = (w[k] * factor).to(torch.bfloat16).float()
-    return tweak
 
 
 def test_chunk_edges_and_page_borders_with_peaked_scores(seq):
