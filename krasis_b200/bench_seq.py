@@ -244,7 +244,7 @@ def run_megolorn(args, peaks):
         hc = HybridMoEConfig(hidden_size=W, num_attention_heads=16, num_key_value_heads=2, gqa_head_dim=256, rope_theta=1000000.0,
                              rms_norm_eps=1e-6)
         src = SyntheticWeights(hc, dev, 0)
-        ac = SimpleNamespace(**{f: getattr(hc, f) for f in hc.__dataclass_fields__})
+        ac = SimpleNamespace(**{f: getattr(hc, f) for f in hc.__dataclass_fields__}, rotary_dim=hc.rotary_dim)
         gqa = GQAAttention(ac, 0, src.attention(0, "full_attention"), dev, max_tokens=tokens)
         kv = PagedKVCache.from_config(ac, 1, dev, max_pages=tokens // 16 + 2)
         pos = torch.arange(tokens, dtype=torch.int32, device=dev)

@@ -359,6 +359,53 @@ class RoutedExperts:
             if "shared_gate" in weights else None
         self.tile = ops.load().kb2_seq_moe_tile_rows()
         self.gemv_max_tokens = 8
+        # bfloat16 steps that bring at least this many rows per expert on average run each expert's rows on the tcgen05 GEMM
+        self.tc_min_rows_per_expert = 64
+
+    def _bin(self, ids, slots):
+        """Device tables of the binned order (see kb2_seq_moe_bin); `head` = [counts | offs] for one read-back."""
+        E, tile, dev = self.E, self.tile, ids.device
+        max_rows = (slots + E * (tile - 1) + tile - 1) // tile * tile
+        max_tiles = max_rows // tile
+        ints = torch.empty(3 * E + 2 + max_tiles + max_rows + slots, dtype=torch.int32, device=dev)
+        t = {"counts": ints[:E], "offs": ints[E:2 * E + 1], "cursor": ints[2 * E + 1:3 * E + 1], "n_tiles": ints[3 * E + 1:3 * E + 2],
+             "tile_expert": ints[3 * E + 2:3 * E + 2 + max_tiles], "slot_row": ints[3 * E + 2 + max_tiles:3 * E + 2 + max_tiles + max_rows],
+             "pos": ints[3 * E + 2 + max_tiles + max_rows:], "head": ints[:2 * E + 1], "max_rows": max_rows, "max_tiles": max_tiles}
+        ops.check(ops.load().kb2_seq_moe_bin(ids.data_ptr(), slots, E, t["counts"].data_ptr(), t["offs"].data_ptr(), t["cursor"].data_ptr(),
+                                             t["tile_expert"].data_ptr(), t["n_tiles"].data_ptr(), t["slot_row"].data_ptr(), max_rows,
+                                             t["pos"].data_ptr(), torch.cuda.current_stream(dev).cuda_stream))
+        return t
+
+    def _tensor_core_ok(self, h, slots):
+        W = h.shape[1]
+        return (self.dtype == torch.bfloat16 and h.dtype == torch.bfloat16 and h.is_contiguous() and W % 64 == 0 and self.F % 64 == 0
+                and slots >= self.tc_min_rows_per_expert * self.E and not torch.cuda.is_current_stream_capturing() and bool(_core_lib()))
+
+    def _forward_tensor_core(self, h, ids, slots):
+        """Long bfloat16 steps: rows gathered into the binned order, then one tcgen05 GEMM per expert and projection on its run of
+        rows.  The run lengths are read back from the device (one synchronisation per call)."""
+        from . import capi
+        core, E, top, W, F, dev = _core_lib(), self.E, self.top, h.shape[1], self.F, h.device
+        s = torch.cuda.current_stream(dev).cuda_stream
+        t = self._bin(ids, slots)
+        head = t["head"].tolist()
+        counts, offs = head[:E], head[E:]
+        total = offs[E]
+        src = torch.div(t["slot_row"][:total].clamp_min(0), top, rounding_mode="floor").to(torch.int64)
+        xs = h.index_select(0, src)
+        gu = torch.empty((total, 2 * F), dtype=torch.bfloat16, device=dev)
+        di = dev.index or 0
+        for e in range(E):
+            if counts[e]:
+                capi.check(core.kb2_linear_bf16(xs[offs[e]:].data_ptr(), self.w_gu[e].data_ptr(), None, gu[offs[e]:].data_ptr(), counts[e], 2 * F, W,
+                                                0, di, s))
+        act = ops.glu(gu, torch.bfloat16, ops.GLU_SILU)
+        y = torch.empty((total, W), dtype=torch.float32, device=dev)
+        for e in range(E):
+            if counts[e]:
+                capi.check(core.kb2_linear_bf16(act[offs[e]:].data_ptr(), self.w_down[e].data_ptr(), None, y[offs[e]:].data_ptr(), counts[e], W, F,
+                                                1, di, s))
+        return y, t["pos"]
 
     def route(self, h: torch.Tensor):
         return ops.route(lin(h, self.w_router, torch.float32), self.correction, self.top, self.groups, self.keep, self.score, self.renorm,
@@ -373,25 +420,19 @@ class RoutedExperts:
         y = pos = None
         if E and T <= self.gemv_max_tokens:
             F2 = self.w_gu.shape[1]
-            gu = torch.zeros((slots, F2), dtype=dt, device=dev)
+            gu = torch.empty((slots, F2), dtype=dt, device=dev)
             ops.check(lib.kb2_seq_moe_gemv(h.data_ptr(), ops.dt_code(h.dtype), h.stride(0), top, ids.data_ptr(), E, self.w_gu.data_ptr(), dtc, W,
                                            F2 * W, gu.data_ptr(), dtc, F2, slots, F2, W, s))
             act = ops.glu(gu, dt, ops.GLU_SILU)
             y = torch.empty((slots, W), dtype=torch.float32, device=dev)
             ops.check(lib.kb2_seq_moe_gemv(act.data_ptr(), dtc, self.F, 1, ids.data_ptr(), E, self.w_down.data_ptr(), dtc, self.F, W * self.F,
                                            y.data_ptr(), 0, W, slots, W, self.F, s))
+        elif E and self._tensor_core_ok(h, slots):
+            y, pos = self._forward_tensor_core(h, ids, slots)
         elif E:
             F2, tile = self.w_gu.shape[1], self.tile
-            max_rows = (slots + E * (tile - 1) + tile - 1) // tile * tile
-            max_tiles = max_rows // tile
-            ints = torch.empty(3 * E + 2 + max_tiles + max_rows + slots, dtype=torch.int32, device=dev)
-            counts, offs, cursor = ints[:E], ints[E:2 * E + 1], ints[2 * E + 1:3 * E + 1]
-            n_tiles = ints[3 * E + 1:3 * E + 2]
-            tile_expert = ints[3 * E + 2:3 * E + 2 + max_tiles]
-            slot_row = ints[3 * E + 2 + max_tiles:3 * E + 2 + max_tiles + max_rows]
-            pos = ints[3 * E + 2 + max_tiles + max_rows:]
-            ops.check(lib.kb2_seq_moe_bin(ids.data_ptr(), slots, E, counts.data_ptr(), offs.data_ptr(), cursor.data_ptr(), tile_expert.data_ptr(),
-                                          n_tiles.data_ptr(), slot_row.data_ptr(), max_rows, pos.data_ptr(), s))
+            t = self._bin(ids, slots)
+            max_rows, max_tiles, n_tiles, tile_expert, slot_row, pos = t["max_rows"], t["max_tiles"], t["n_tiles"], t["tile_expert"], t["slot_row"], t["pos"]
             gu = torch.empty((max_rows, F2), dtype=dt, device=dev)
             ops.check(lib.kb2_seq_moe_gemm(h.data_ptr(), ops.dt_code(h.dtype), h.stride(0), slot_row.data_ptr(), top, self.w_gu.data_ptr(), dtc, W,
                                            F2 * W, gu.data_ptr(), dtc, F2, F2, W, tile_expert.data_ptr(), n_tiles.data_ptr(), max_tiles, s))

@@ -290,6 +290,31 @@ def test_routed_experts_alone(seq, T):
         close(alone.cpu().numpy(), got[T - 1:].cpu().numpy().astype(np.float64), 1e-5, "last row alone")
 
 
+def test_routed_experts_on_the_tensor_core_gemm(seq):
+    """bfloat16 steps with many rows per expert gather the rows per expert and run one tcgen05 GEMM per expert and projection:
+    against the oracle and against the binned tile kernels, with one expert that gets no token at all."""
+    from krasis_b200.build import build as build_core
+    from krasis_b200.mixers import RoutedExperts
+    build_core()
+    W, F, E, ident, T = 64, 128, 5, 1, 700
+    mlp = moe(experts=E, identity=ident, top=2, groups=3, keep=2, ff=F, shared=0)
+    w = {"router": rnd(E + ident, W, seed=1, sd=0.8), "correction": rnd(E + ident, seed=2, sd=0.02)}
+    w["correction"][3] = -10.0                                           # expert 3 is never chosen
+    for e in range(E):
+        w.update({f"e{e}.gate": rnd(F, W, seed=10 + e, sd=0.2), f"e{e}.up": rnd(F, W, seed=30 + e, sd=0.2), f"e{e}.down": rnd(W, F, seed=50 + e, sd=0.2)})
+    h = rnd(T, W, seed=7)
+    want = O.mixture(h.numpy().astype(np.float64), f64(w), mlp)
+    mod = RoutedExperts({k.replace(".", "_"): v for k, v in w.items()}, E, ident, 2, torch.bfloat16, "cuda:0", groups=3, keep=2)
+    hb = h.cuda().to(torch.bfloat16)
+    assert mod._tensor_core_ok(hb, T * 2)
+    fast = mod.forward(hb).cpu().numpy()
+    mod.tc_min_rows_per_expert = 1 << 30
+    plain = mod.forward(hb).cpu().numpy()
+    close(plain, want, 2e-2, "tile kernels against the oracle")
+    close(fast, want, 2e-2, "tensor-core GEMMs against the oracle")
+    close(fast, plain.astype(np.float64), 1e-2, "tensor-core GEMMs against the tile kernels")
+
+
 def test_residual_sum_and_norm_without_bias(seq):
     T, W = 5, 77
     x, y, y2, wn = rnd(T, W, seed=1), rnd(T, W, seed=2), rnd(T, W, seed=3), 1 + rnd(W, seed=4, sd=0.1)
