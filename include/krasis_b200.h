@@ -219,6 +219,13 @@ KB2_API int64_t kb2_launch_count(const kb2_engine* e);
 KB2_API int kb2_linear_bf16(const void* x_dev, const void* w_dev, const float* bias_dev, void* out_dev, int32_t M,
                             int32_t N, int32_t K, int32_t out_f32, int32_t device, void* stream);
 
+/* Grouped form of kb2_linear_bf16 for rows binned per group in tiles of 128 (routed experts): w [groups][N][K], row tile i of x
+ * (rows 128 i .. 128 i + 127) is multiplied by w[tile_group_dev[i]], and only the first num_row_tiles_dev[0] row tiles are computed
+ * (both tables live on the device: no host round trip).  x [M][K], out [M][N] bf16 or fp32, M an upper bound of the binned rows. */
+KB2_API int kb2_linear_bf16_grouped(const void* x_dev, const void* w_dev, void* out_dev, int32_t M, int32_t N, int32_t K, int32_t out_f32,
+                                    const int32_t* tile_group_dev, const int32_t* num_row_tiles_dev, int32_t groups, int32_t device,
+                                    void* stream);
+
 /* flashinfer.norm.rmsnorm (residual_dev == NULL) / fused_add_rmsnorm (residual_dev != NULL: residual += x, in place)
  * as used at python/krasis/layer.py:163-183,283-308.  x, residual, out: [M][H] bf16 (out may alias x); weight [H] f32. */
 KB2_API int kb2_rmsnorm(void* x_dev, void* residual_dev, const float* weight_dev, void* out_dev, int32_t M, int32_t H,

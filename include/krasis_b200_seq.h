@@ -121,17 +121,17 @@ KB2SEQ_API int kb2_seq_route(const float* z, long long ldz, int T, int E, const 
                              int top, int renorm, float out_scale, int* ids, float* weights, void* stream);
 
 /* Routed experts.  moe_bin: slots = T * top entries of ids; ids outside [0, E) are left out (identity experts).  Each expert's slots
- * form a run of rows padded to whole tiles of kb2_seq_moe_tile_rows(): offs [E + 1], tile_expert [max_rows / tile], n_tiles [1],
+ * form a run of rows padded to whole tiles of tile_rows (a multiple of kb2_seq_moe_tile_rows()): offs [E + 1], tile_expert [max_rows / tile], n_tiles [1],
  * slot_row [max_rows] (row -> slot, -1 padding), pos_of_slot [slots] (slot -> row, -1 left out); counts, cursor [E] are scratch;
  * max_rows >= slots + E * (tile - 1). */
 KB2SEQ_API int kb2_seq_moe_tile_rows(void);
-KB2SEQ_API int kb2_seq_moe_bin(const int* ids, long long slots, int E, int* counts, int* offs, int* cursor, int* tile_expert, int* n_tiles,
-                               int* slot_row, long long max_rows, int* pos_of_slot, void* stream);
+KB2SEQ_API int kb2_seq_moe_bin(const int* ids, long long slots, int E, int tile_rows, int* counts, int* offs, int* cursor, int* tile_expert,
+                               int* n_tiles, int* slot_row, long long max_rows, int* pos_of_slot, void* stream);
 /* C[p, :] = A[src(p), :] * B[tile_expert[p / tile]]^T (B: [experts][N][ldb], expert stride sB) for the rows of the first n_tiles[0] tiles;
  * src(p) = p, or row_map[p] / div when row_map is given (negative: zeros). */
 KB2SEQ_API int kb2_seq_moe_gemm(const void* A, int dtA, long long lda, const int* row_map, int div, const void* B, int dtB, long long ldb,
                                 long long sB, void* C, int dtC, long long ldc, int N, int K, const int* tile_expert, const int* n_tiles,
-                                int max_tiles, void* stream);
+                                int max_tiles, int tile_rows, void* stream);
 /* Few slots, no binning: C[slot, :] = A[slot / div, :] * B[ids[slot]]^T; slots with ids outside [0, E) are skipped. */
 KB2SEQ_API int kb2_seq_moe_gemv(const void* A, int dtA, long long lda, int div, const int* ids, int E, const void* B, int dtB, long long ldb,
                                 long long sB, void* C, int dtC, long long ldc, int slots, int N, int K, void* stream);

@@ -14,6 +14,8 @@ struct GdnDims {
   float eps, scale;
   int ba_ld;
 };
+cudaError_t launch_dense_gemm_grouped(const void* x, const void* w, void* out, int M, int N, int K, long long ldo, bool out_f32,
+                                      const int* tile_group, const int* m_tiles_dev, int groups, int num_sms, cudaStream_t s);
 cudaError_t launch_dense_gemm(const void* x, const void* w, void* out, const float* bias, int M, int N, int K,
                               long long ldo, bool out_f32, int num_sms, cudaStream_t s);
 cudaError_t launch_gdn_core(const GdnDims& d, const void* qkvz, const void* ba, const void* conv_w, void* conv_state,
@@ -137,6 +139,18 @@ KB2_API int kb2_linear_bf16(const void* x_dev, const void* w_dev, const float* b
   if (M <= 0 || N <= 0 || K <= 0 || K % 64 || N % 16) return failf(KB2_ERR_VALUE, "linear: need M>0, K %% 64 == 0, N %% 16 == 0 (M=%d N=%d K=%d)", M, N, K);
   CUDA_TRY(cudaSetDevice(device));
   CUDA_TRY(launch_dense_gemm(x_dev, w_dev, out_dev, bias_dev, M, N, K, N, out_f32 != 0, device_sms(device), (cudaStream_t)stream));
+  return KB2_OK;
+}
+
+KB2_API int kb2_linear_bf16_grouped(const void* x_dev, const void* w_dev, void* out_dev, int32_t M, int32_t N, int32_t K, int32_t out_f32,
+                                    const int32_t* tile_group_dev, const int32_t* num_row_tiles_dev, int32_t groups, int32_t device,
+                                    void* stream) {
+  if (!x_dev || !w_dev || !out_dev || !tile_group_dev || !num_row_tiles_dev) return failf(KB2_ERR_VALUE, "null argument");
+  if (M <= 0 || N <= 0 || K <= 0 || K % 64 || N % 16 || groups <= 0)
+    return failf(KB2_ERR_VALUE, "grouped linear: need M>0, K %% 64 == 0, N %% 16 == 0, groups > 0 (M=%d N=%d K=%d)", M, N, K);
+  CUDA_TRY(cudaSetDevice(device));
+  CUDA_TRY(launch_dense_gemm_grouped(x_dev, w_dev, out_dev, M, N, K, N, out_f32 != 0, tile_group_dev, num_row_tiles_dev, groups,
+                                     device_sms(device), (cudaStream_t)stream));
   return KB2_OK;
 }
 

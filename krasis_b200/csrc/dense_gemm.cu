@@ -29,7 +29,10 @@ template <int MODE>
 __global__ void __launch_bounds__(kDThreads, 1)
     dense_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUtensorMap tmap_w,
                       void* __restrict__ out, const float* __restrict__ bias, int M, int N, int K, long long ldo,
-                      const float* __restrict__ row_scale, const __nv_bfloat16* __restrict__ col_scale, CombineScatter sc) {
+                      const float* __restrict__ row_scale, const __nv_bfloat16* __restrict__ col_scale, CombineScatter sc,
+                      // grouped form (routed experts on binned rows): W holds `groups` matrices of N rows one after the other, row tile i
+                      // (128 rows of X) multiplies matrix tile_group[i], and only the first m_tiles_dev[0] row tiles exist
+                      const int* __restrict__ tile_group = nullptr, const int* __restrict__ m_tiles_dev = nullptr) {
   constexpr bool kOutF32 = MODE == 1;
   constexpr int kElemsPerBlock = MODE == 2 ? 128 : 64;     // 128 B of K per smem row
   extern __shared__ __align__(1024) uint8_t smem[];
@@ -41,7 +44,8 @@ __global__ void __launch_bounds__(kDThreads, 1)
   // warp index through a shuffle so that the role branches are provably warp-uniform: the single-thread instructions (TMA, tcgen05.mma,
   // commit) then take their operands from uniform registers instead of an ELECT + R2UR.BROADCAST loop per instruction
   const int warp = __shfl_sync(0xffffffffu, (int)(threadIdx.x >> 5), 0), lane = threadIdx.x & 31;
-  const int n_tiles = (N + kDTileN - 1) / kDTileN, m_tiles = (M + kDTileM - 1) / kDTileM;
+  const int n_tiles = (N + kDTileN - 1) / kDTileN, m_tiles_max = (M + kDTileM - 1) / kDTileM;
+  const int m_tiles = m_tiles_dev != nullptr ? min(m_tiles_max, m_tiles_dev[0]) : m_tiles_max;
   const int total = n_tiles * m_tiles;
   const int nkb = K / kElemsPerBlock;
 
@@ -72,7 +76,8 @@ __global__ void __launch_bounds__(kDThreads, 1)
       int stage = 0;
       uint32_t phase = 0;
       for (int t = blockIdx.x; t < total; t += gridDim.x) {
-        const int m0 = (t / n_tiles) * kDTileM, n0 = (t % n_tiles) * kDTileN;
+        const int m0 = (t / n_tiles) * kDTileM;
+        const int n0 = (t % n_tiles) * kDTileN + (tile_group != nullptr ? tile_group[t / n_tiles] * N : 0);   // row of W
         for (int kb = 0; kb < nkb; ++kb) {
           mbar_wait(&empty[stage], phase ^ 1);
           uint8_t* a = smem + stage * kDStage;
@@ -229,6 +234,29 @@ cudaError_t launch_dense_gemm_scatter(const void* x, const void* w, void* out, c
     dense_gemm_kernel<1><<<grid, kDThreads, kDSmem, s>>>(tx, tw, out, bias, M, N, K, ldo, nullptr, nullptr, CombineScatter{});
   else
     dense_gemm_kernel<0><<<grid, kDThreads, kDSmem, s>>>(tx, tw, out, bias, M, N, K, ldo, nullptr, nullptr, sc);
+  return cudaGetLastError();
+}
+
+// Grouped form: X [M][K] rows binned in tiles of 128 per group, W [groups * N][K], out [M][ldo]; tile_group / m_tiles_dev on the device.
+cudaError_t launch_dense_gemm_grouped(const void* x, const void* w, void* out, int M, int N, int K, long long ldo, bool out_f32,
+                                      const int* tile_group, const int* m_tiles_dev, int groups, int num_sms, cudaStream_t s) {
+  KernelSpan ks(K_DENSE_BF16, s);
+  if (K % kBlockK || N % 16 || M <= 0 || groups <= 0 || !tile_group || !m_tiles_dev) return cudaErrorInvalidValue;
+  alignas(64) CUtensorMap tx, tw;
+  cudaError_t e = make_tmap_bf16_rows(&tx, x, M, K, 128);
+  if (e != cudaSuccess) return e;
+  e = make_tmap_bf16_rows(&tw, w, (long long)groups * N, K, 128);
+  if (e != cudaSuccess) return e;
+  e = dense_configure();
+  if (e != cudaSuccess) return e;
+  const int total = ((M + kDTileM - 1) / kDTileM) * ((N + kDTileN - 1) / kDTileN);
+  const int grid = total < num_sms ? total : num_sms;
+  if (out_f32)
+    dense_gemm_kernel<1><<<grid, kDThreads, kDSmem, s>>>(tx, tw, out, nullptr, M, N, K, ldo, nullptr, nullptr, CombineScatter{}, tile_group,
+                                                        m_tiles_dev);
+  else
+    dense_gemm_kernel<0><<<grid, kDThreads, kDSmem, s>>>(tx, tw, out, nullptr, M, N, K, ldo, nullptr, nullptr, CombineScatter{}, tile_group,
+                                                        m_tiles_dev);
   return cudaGetLastError();
 }
 

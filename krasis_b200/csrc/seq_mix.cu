@@ -401,22 +401,22 @@ __global__ void moe_count_kernel(const int* __restrict__ ids, long long slots, i
     if (e >= 0 && e < E) atomicAdd(&counts[e], 1);
   }
 }
-// One block: offs[e] = first row of expert e's run, runs padded to whole tiles; tile_expert[tile]; n_tiles[0]; cursor[e] = 0.
-__global__ void moe_plan_kernel(const int* __restrict__ counts, int E, int* __restrict__ offs, int* __restrict__ cursor,
+// One block: offs[e] = first row of expert e's run, runs padded to whole tiles of tile_rows; tile_expert[tile]; n_tiles[0]; cursor[e] = 0.
+__global__ void moe_plan_kernel(const int* __restrict__ counts, int E, int tile_rows, int* __restrict__ offs, int* __restrict__ cursor,
                                 int* __restrict__ tile_expert, int* __restrict__ n_tiles) {
   if (threadIdx.x == 0) {
     int tiles = 0;
     for (int e = 0; e < E; ++e) {
-      offs[e] = tiles * kMoeBM;
-      tiles += (counts[e] + kMoeBM - 1) / kMoeBM;
+      offs[e] = tiles * tile_rows;
+      tiles += (counts[e] + tile_rows - 1) / tile_rows;
     }
-    offs[E] = tiles * kMoeBM;
+    offs[E] = tiles * tile_rows;
     n_tiles[0] = tiles;
   }
   __syncthreads();
   for (int e = threadIdx.x; e < E; e += blockDim.x) {
     cursor[e] = 0;
-    for (int tl = offs[e] / kMoeBM; tl < offs[e + 1] / kMoeBM; ++tl) tile_expert[tl] = e;
+    for (int tl = offs[e] / tile_rows; tl < offs[e + 1] / tile_rows; ++tl) tile_expert[tl] = e;
   }
 }
 // slot_row[p] = slot (t * top + k) that sits at row p of the binned order (-1: padding); pos_of_slot[slot] = p (-1: not routed here)
@@ -439,12 +439,12 @@ template <typename TA, typename TB, typename TC>
 __global__ void __launch_bounds__(256) moe_gemm_kernel(const TA* __restrict__ A, long long lda, const int* __restrict__ row_map, int div,
                                                        const TB* __restrict__ B, long long ldb, long long sB, TC* __restrict__ C,
                                                        long long ldc, int N, int K, const int* __restrict__ tile_expert,
-                                                       const int* __restrict__ n_tiles) {
-  constexpr int BM = kMoeBM, BN = 64, BK = 16;
-  if ((int)blockIdx.y >= n_tiles[0]) return;
+                                                       const int* __restrict__ n_tiles, int tile_rows) {
+  constexpr int BM = kMoeBM, BN = 64, BK = 16;           // tile_rows is a multiple of BM: a block never straddles two experts
+  if ((long long)blockIdx.y * BM >= (long long)n_tiles[0] * tile_rows) return;
   __shared__ float As[BK][BM + 4], Bs[BK][BN + 4];
   __shared__ long long src[BM];
-  B += (long long)tile_expert[blockIdx.y] * sB;
+  B += (long long)tile_expert[(long long)blockIdx.y * BM / tile_rows] * sB;
   const int tid = threadIdx.x, tx = tid & 15, ty = tid >> 4;
   const long long m0 = (long long)blockIdx.y * BM;
   const int n0 = blockIdx.x * BN;
@@ -638,10 +638,10 @@ KB2SEQ_API int kb2_seq_route(const float* z, long long ldz, int T, int E, const 
 
 KB2SEQ_API int kb2_seq_moe_tile_rows(void) { return kMoeBM; }
 
-KB2SEQ_API int kb2_seq_moe_bin(const int* ids, long long slots, int E, int* counts, int* offs, int* cursor, int* tile_expert, int* n_tiles,
-                               int* slot_row, long long max_rows, int* pos_of_slot, void* stream) {
+KB2SEQ_API int kb2_seq_moe_bin(const int* ids, long long slots, int E, int tile_rows, int* counts, int* offs, int* cursor, int* tile_expert,
+                               int* n_tiles, int* slot_row, long long max_rows, int* pos_of_slot, void* stream) {
   if (!ids || !counts || !offs || !cursor || !tile_expert || !n_tiles || !slot_row || !pos_of_slot || slots <= 0 || E <= 0 ||
-      max_rows < slots + (long long)E * (kMoeBM - 1))
+      tile_rows <= 0 || tile_rows % kMoeBM || max_rows < slots + (long long)E * (tile_rows - 1))
     return failf(KB2SEQ_ERR_VALUE, "moe_bin: bad argument");
   cudaStream_t s = (cudaStream_t)stream;
   SEQ_CUDA(cudaMemsetAsync(counts, 0, (size_t)E * 4, s));
@@ -649,7 +649,7 @@ KB2SEQ_API int kb2_seq_moe_bin(const int* ids, long long slots, int E, int* coun
   const unsigned blocks = (unsigned)((slots + 255) / 256 > 1024 ? 1024 : (slots + 255) / 256);
   moe_count_kernel<<<blocks, 256, 0, s>>>(ids, slots, E, counts);
   SEQ_LAUNCHED();
-  moe_plan_kernel<<<1, 256, 0, s>>>(counts, E, offs, cursor, tile_expert, n_tiles);
+  moe_plan_kernel<<<1, 256, 0, s>>>(counts, E, tile_rows, offs, cursor, tile_expert, n_tiles);
   SEQ_LAUNCHED();
   moe_scatter_kernel<<<blocks, 256, 0, s>>>(ids, slots, E, offs, cursor, slot_row, pos_of_slot);
   SEQ_LAUNCHED();
@@ -658,15 +658,15 @@ KB2SEQ_API int kb2_seq_moe_bin(const int* ids, long long slots, int E, int* coun
 
 KB2SEQ_API int kb2_seq_moe_gemm(const void* A, int dtA, long long lda, const int* row_map, int div, const void* B, int dtB, long long ldb,
                                 long long sB, void* C, int dtC, long long ldc, int N, int K, const int* tile_expert, const int* n_tiles,
-                                int max_tiles, void* stream) {
-  if (!A || !B || !C || !tile_expert || !n_tiles || N <= 0 || K <= 0 || max_tiles <= 0 || max_tiles > 65535 || div <= 0 || bad_dt(dtA) ||
-      bad_dt(dtB) || bad_dt(dtC))
+                                int max_tiles, int tile_rows, void* stream) {
+  if (!A || !B || !C || !tile_expert || !n_tiles || N <= 0 || K <= 0 || max_tiles <= 0 || tile_rows <= 0 || tile_rows % kMoeBM ||
+      (long long)max_tiles * (tile_rows / kMoeBM) > 65535 || div <= 0 || bad_dt(dtA) || bad_dt(dtB) || bad_dt(dtC))
     return failf(KB2SEQ_ERR_VALUE, "moe_gemm: bad argument");
   cudaStream_t s = (cudaStream_t)stream;
-  dim3 grid((N + 63) / 64, max_tiles);
+  dim3 grid((N + 63) / 64, max_tiles * (tile_rows / kMoeBM));
 #define G(TA, TB, TC)                                                                                                          \
   moe_gemm_kernel<TA, TB, TC><<<grid, 256, 0, s>>>((const TA*)A, lda, row_map, div, (const TB*)B, ldb, sB, (TC*)C, ldc, N, K, tile_expert, \
-                                                   n_tiles)
+                                                   n_tiles, tile_rows)
   switch (dtA * 4 + dtB * 2 + dtC) {
     case 0: G(float, float, float); break;
     case 1: G(float, float, bf16); break;

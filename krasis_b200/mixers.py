@@ -359,19 +359,19 @@ class RoutedExperts:
             if "shared_gate" in weights else None
         self.tile = ops.load().kb2_seq_moe_tile_rows()
         self.gemv_max_tokens = 8
-        # bfloat16 steps that bring at least this many rows per expert on average run each expert's rows on the tcgen05 GEMM
-        self.tc_min_rows_per_expert = 64
+        # bfloat16 steps that bring at least this many rows per expert on average run on the grouped tcgen05 GEMM (128-row tiles)
+        self.tc_min_rows_per_expert = 16
 
-    def _bin(self, ids, slots):
-        """Device tables of the binned order (see kb2_seq_moe_bin); `head` = [counts | offs] for one read-back."""
-        E, tile, dev = self.E, self.tile, ids.device
+    def _bin(self, ids, slots, tile):
+        """Device tables of the binned order with runs padded to `tile` rows (see kb2_seq_moe_bin)."""
+        E, dev = self.E, ids.device
         max_rows = (slots + E * (tile - 1) + tile - 1) // tile * tile
         max_tiles = max_rows // tile
         ints = torch.empty(3 * E + 2 + max_tiles + max_rows + slots, dtype=torch.int32, device=dev)
         t = {"counts": ints[:E], "offs": ints[E:2 * E + 1], "cursor": ints[2 * E + 1:3 * E + 1], "n_tiles": ints[3 * E + 1:3 * E + 2],
              "tile_expert": ints[3 * E + 2:3 * E + 2 + max_tiles], "slot_row": ints[3 * E + 2 + max_tiles:3 * E + 2 + max_tiles + max_rows],
-             "pos": ints[3 * E + 2 + max_tiles + max_rows:], "head": ints[:2 * E + 1], "max_rows": max_rows, "max_tiles": max_tiles}
-        ops.check(ops.load().kb2_seq_moe_bin(ids.data_ptr(), slots, E, t["counts"].data_ptr(), t["offs"].data_ptr(), t["cursor"].data_ptr(),
+             "pos": ints[3 * E + 2 + max_tiles + max_rows:], "max_rows": max_rows, "max_tiles": max_tiles}
+        ops.check(ops.load().kb2_seq_moe_bin(ids.data_ptr(), slots, E, tile, t["counts"].data_ptr(), t["offs"].data_ptr(), t["cursor"].data_ptr(),
                                              t["tile_expert"].data_ptr(), t["n_tiles"].data_ptr(), t["slot_row"].data_ptr(), max_rows,
                                              t["pos"].data_ptr(), torch.cuda.current_stream(dev).cuda_stream))
         return t
@@ -379,32 +379,26 @@ class RoutedExperts:
     def _tensor_core_ok(self, h, slots):
         W = h.shape[1]
         return (self.dtype == torch.bfloat16 and h.dtype == torch.bfloat16 and h.is_contiguous() and W % 64 == 0 and self.F % 64 == 0
-                and slots >= self.tc_min_rows_per_expert * self.E and not torch.cuda.is_current_stream_capturing() and bool(_core_lib()))
+                and slots >= self.tc_min_rows_per_expert * self.E and bool(_core_lib()))
 
     def _forward_tensor_core(self, h, ids, slots):
-        """Long bfloat16 steps: rows gathered into the binned order, then one tcgen05 GEMM per expert and projection on its run of
-        rows.  The run lengths are read back from the device (one synchronisation per call)."""
+        """Long bfloat16 steps: rows gathered into the binned order (runs padded to the 128-row tiles of the tcgen05 GEMM), then ONE
+        grouped GEMM per projection: every row tile multiplies its expert's matrix, picked from the device-side tile table, and only
+        the tiles that exist are computed — no host round trip."""
         from . import capi
         core, E, top, W, F, dev = _core_lib(), self.E, self.top, h.shape[1], self.F, h.device
         s = torch.cuda.current_stream(dev).cuda_stream
-        t = self._bin(ids, slots)
-        head = t["head"].tolist()
-        counts, offs = head[:E], head[E:]
-        total = offs[E]
-        src = torch.div(t["slot_row"][:total].clamp_min(0), top, rounding_mode="floor").to(torch.int64)
+        t = self._bin(ids, slots, 128)
+        rows, di = t["max_rows"], dev.index or 0
+        src = torch.div(t["slot_row"].clamp_min(0), top, rounding_mode="floor").to(torch.int64)     # padding rows read token 0; never used
         xs = h.index_select(0, src)
-        gu = torch.empty((total, 2 * F), dtype=torch.bfloat16, device=dev)
-        di = dev.index or 0
-        for e in range(E):
-            if counts[e]:
-                capi.check(core.kb2_linear_bf16(xs[offs[e]:].data_ptr(), self.w_gu[e].data_ptr(), None, gu[offs[e]:].data_ptr(), counts[e], 2 * F, W,
-                                                0, di, s))
-        act = ops.glu(gu, torch.bfloat16, ops.GLU_SILU)
-        y = torch.empty((total, W), dtype=torch.float32, device=dev)
-        for e in range(E):
-            if counts[e]:
-                capi.check(core.kb2_linear_bf16(act[offs[e]:].data_ptr(), self.w_down[e].data_ptr(), None, y[offs[e]:].data_ptr(), counts[e], W, F,
-                                                1, di, s))
+        gu = torch.empty((rows, 2 * F), dtype=torch.bfloat16, device=dev)
+        capi.check(core.kb2_linear_bf16_grouped(xs.data_ptr(), self.w_gu.data_ptr(), gu.data_ptr(), rows, 2 * F, W, 0, t["tile_expert"].data_ptr(),
+                                                t["n_tiles"].data_ptr(), E, di, s))
+        act = ops.glu(gu, torch.bfloat16, ops.GLU_SILU, n_tiles=t["n_tiles"], tile_rows=128)
+        y = torch.empty((rows, W), dtype=torch.float32, device=dev)
+        capi.check(core.kb2_linear_bf16_grouped(act.data_ptr(), self.w_down.data_ptr(), y.data_ptr(), rows, W, F, 1, t["tile_expert"].data_ptr(),
+                                                t["n_tiles"].data_ptr(), E, di, s))
         return y, t["pos"]
 
     def route(self, h: torch.Tensor):
@@ -431,15 +425,15 @@ class RoutedExperts:
             y, pos = self._forward_tensor_core(h, ids, slots)
         elif E:
             F2, tile = self.w_gu.shape[1], self.tile
-            t = self._bin(ids, slots)
+            t = self._bin(ids, slots, tile)
             max_rows, max_tiles, n_tiles, tile_expert, slot_row, pos = t["max_rows"], t["max_tiles"], t["n_tiles"], t["tile_expert"], t["slot_row"], t["pos"]
             gu = torch.empty((max_rows, F2), dtype=dt, device=dev)
             ops.check(lib.kb2_seq_moe_gemm(h.data_ptr(), ops.dt_code(h.dtype), h.stride(0), slot_row.data_ptr(), top, self.w_gu.data_ptr(), dtc, W,
-                                           F2 * W, gu.data_ptr(), dtc, F2, F2, W, tile_expert.data_ptr(), n_tiles.data_ptr(), max_tiles, s))
+                                           F2 * W, gu.data_ptr(), dtc, F2, F2, W, tile_expert.data_ptr(), n_tiles.data_ptr(), max_tiles, tile, s))
             act = ops.glu(gu, dt, ops.GLU_SILU, n_tiles=n_tiles, tile_rows=tile)
             y = torch.empty((max_rows, W), dtype=torch.float32, device=dev)
             ops.check(lib.kb2_seq_moe_gemm(act.data_ptr(), dtc, self.F, None, 1, self.w_down.data_ptr(), dtc, self.F, W * self.F, y.data_ptr(), 0,
-                                           W, W, self.F, tile_expert.data_ptr(), n_tiles.data_ptr(), max_tiles, s))
+                                           W, W, self.F, tile_expert.data_ptr(), n_tiles.data_ptr(), max_tiles, tile, s))
         shared = self.shared.forward(h) if self.shared is not None else None
         out = torch.empty((T, W), dtype=torch.float32, device=dev)
         ops.check(lib.kb2_seq_moe_combine(ops._ptr(y), ops._ptr(pos), ids.data_ptr(), wts.data_ptr(), T, top, E, self.ident, h.data_ptr(),

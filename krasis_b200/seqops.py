@@ -32,8 +32,8 @@ SIGNATURES = {
     "kb2_seq_glu": (_I, [_P, _I, _L, _P, _I, _L, _I, _I, _F, _F, _P, _I, _P]),
     "kb2_seq_route": (_I, [_P, _L, _I, _I, _P, _I, _I, _I, _I, _I, _F, _P, _P, _P]),
     "kb2_seq_moe_tile_rows": (_I, []),
-    "kb2_seq_moe_bin": (_I, [_P, _L, _I, _P, _P, _P, _P, _P, _P, _L, _P, _P]),
-    "kb2_seq_moe_gemm": (_I, [_P, _I, _L, _P, _I, _P, _I, _L, _L, _P, _I, _L, _I, _I, _P, _P, _I, _P]),
+    "kb2_seq_moe_bin": (_I, [_P, _L, _I, _I, _P, _P, _P, _P, _P, _P, _L, _P, _P]),
+    "kb2_seq_moe_gemm": (_I, [_P, _I, _L, _P, _I, _P, _I, _L, _L, _P, _I, _L, _I, _I, _P, _P, _I, _I, _P]),
     "kb2_seq_moe_gemv": (_I, [_P, _I, _L, _I, _P, _I, _P, _I, _L, _L, _P, _I, _L, _I, _I, _I, _P]),
     "kb2_seq_moe_combine": (_I, [_P, _P, _P, _P, _I, _I, _I, _I, _P, _I, _P, _P, _I, _P]),
 }

@@ -291,7 +291,7 @@ def test_routed_experts_alone(seq, T):
 
 
 def test_routed_experts_on_the_tensor_core_gemm(seq):
-    """bfloat16 steps with many rows per expert gather the rows per expert and run one tcgen05 GEMM per expert and projection:
+    """bfloat16 steps with many rows per expert gather the rows in binned order and run one grouped tcgen05 GEMM per projection:
     against the oracle and against the binned tile kernels, with one expert that gets no token at all."""
     from krasis_b200.build import build as build_core
     from krasis_b200.mixers import RoutedExperts
