@@ -28,12 +28,15 @@ __global__ void __launch_bounds__(256) head_kv_prep_kernel(float* __restrict__ p
                                                            int rot_dims, const int* __restrict__ positions,
                                                            const int* __restrict__ seq_of, const int* __restrict__ pages, int max_pages,
                                                            int page_size, void* __restrict__ kc, void* __restrict__ vc, int dt_cache) {
+  extern __shared__ float rot_tab[];          // [rot_dims / 2][2]: cos, sin of the token's position, shared by all its vectors
   const long long t = blockIdx.x;
   const int pos = positions[t];
   float* p = proj + t * ldp;
   const long long slot = (long long)pages[(long long)seq_of[t] * max_pages + pos / page_size] * page_size + pos % page_size;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
   const int nq = H * M, nvec = (H + G) * M, half = rot_dims >> 1;
+  for (int j = threadIdx.x; j < half; j += blockDim.x) rot_cs(pos, freq[j], 1.f, &rot_tab[2 * j], &rot_tab[2 * j + 1]);
+  __syncthreads();
   for (int vi = warp; vi < nvec; vi += nw) {
     const bool is_q = vi < nq;
     float* x = p + (long long)vi * d;
@@ -58,8 +61,7 @@ __global__ void __launch_bounds__(256) head_kv_prep_kernel(float* __restrict__ p
         u *= w[2 * j];
         v *= w[2 * j + 1];
       }
-      float c, s;
-      rot_cs(pos, freq[j], 1.f, &c, &s);
+      const float c = rot_tab[2 * j], s = rot_tab[2 * j + 1];
       const float ru = u * c - v * s, rv = v * c + u * s;
       if (is_q) {
         x[2 * j] = ru;
@@ -300,6 +302,27 @@ __global__ void glu_kernel(const void* __restrict__ in, int dt_in, long long ld_
   }
 }
 
+// bf16 in and out, F and ld_in multiples of 8: 16-byte accesses
+__global__ void glu_bf16x8_kernel(const bf16* __restrict__ in, long long ld_in, bf16* __restrict__ out, long long rows, int F, int kind, float limit,
+                                  float alpha, const int* __restrict__ n_tiles, int tile_rows) {
+  if (n_tiles != nullptr) rows = min(rows, (long long)n_tiles[0] * tile_rows);
+  const int F8 = F >> 3;
+  const long long n = rows * F8;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) {
+    const long long r = i / F8;
+    const int f = (int)(i - r * F8) << 3;
+    float a[8], b[8];
+    unpack8(*reinterpret_cast<const uint4*>(in + r * ld_in + f), a);
+    unpack8(*reinterpret_cast<const uint4*>(in + r * ld_in + F + f), b);
+    uint4 o;
+    __nv_bfloat162* po = reinterpret_cast<__nv_bfloat162*>(&o);
+#pragma unroll
+    for (int e = 0; e < 4; ++e)
+      po[e] = __floats2bfloat162_rn(glu_value(a[2 * e], b[2 * e], kind, limit, alpha), glu_value(a[2 * e + 1], b[2 * e + 1], kind, limit, alpha));
+    *reinterpret_cast<uint4*>(out + r * F + f) = o;
+  }
+}
+
 // ------------------------------------------------------------------------------------------------ router
 // A warp per token.  s = softmax(z) (score_kind 0) or sigmoid(z) (1) over the E router outputs; choice c = s + correction; with
 // groups > 1 only the experts of the `keep` groups with the largest maximal choice stay in play; the `top` largest choices are taken
@@ -530,6 +553,31 @@ __global__ void moe_combine_kernel(const float* __restrict__ y, const int* __res
                                    const float* __restrict__ weights, int top, int E, int ident, const void* __restrict__ h, int dt_h,
                                    const float* __restrict__ shared, float* __restrict__ out, int W) {
   const long long t = blockIdx.x;
+  if ((W & 3) == 0 && dt_h == 1) {           // four columns per thread, 16-byte loads of the expert rows; same order of the sum over k
+    for (int d = threadIdx.x * 4; d < W; d += blockDim.x * 4) {
+      float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+      for (int k = 0; k < top; ++k) {
+        const long long slot = t * top + k;
+        const int e = ids[slot];
+        const float w = weights[slot];
+        if (e >= 0 && e < E) {
+          const long long p = pos_of_slot ? pos_of_slot[slot] : slot;
+          const float4 r = *reinterpret_cast<const float4*>(y + p * W + d);
+          v.x = fmaf(w, r.x, v.x); v.y = fmaf(w, r.y, v.y); v.z = fmaf(w, r.z, v.z); v.w = fmaf(w, r.w, v.w);
+        } else if (e >= E && e < E + ident) {
+          const bf16* hp = (const bf16*)h + t * W + d;
+          v.x = fmaf(w, __bfloat162float(hp[0]), v.x); v.y = fmaf(w, __bfloat162float(hp[1]), v.y);
+          v.z = fmaf(w, __bfloat162float(hp[2]), v.z); v.w = fmaf(w, __bfloat162float(hp[3]), v.w);
+        }
+      }
+      if (shared != nullptr) {
+        const float4 r = *reinterpret_cast<const float4*>(shared + t * W + d);
+        v.x += r.x; v.y += r.y; v.z += r.z; v.w += r.w;
+      }
+      *reinterpret_cast<float4*>(out + t * W + d) = v;
+    }
+    return;
+  }
   for (int d = threadIdx.x; d < W; d += blockDim.x) {
     float v = 0.f;
     for (int k = 0; k < top; ++k) {
@@ -562,7 +610,7 @@ KB2SEQ_API int kb2_seq_head_kv_prep(float* proj, long long ldp, int T, int H, in
       rot_dims > d || (rot_dims & 1) || (rot_dims && !freq) || page_size <= 0 || max_pages <= 0 || bad_dt(dt_cache) ||
       (G > 0 && (!kc || !vc)))
     return failf(KB2SEQ_ERR_VALUE, "head_kv_prep: bad argument");
-  head_kv_prep_kernel<<<T, 256, 0, (cudaStream_t)stream>>>(proj, ldp, H, G, M, d, dv, bias, qw, kw, eps, freq, rot_dims, positions, seq_of,
+  head_kv_prep_kernel<<<T, 256, (size_t)rot_dims * 4, (cudaStream_t)stream>>>(proj, ldp, H, G, M, d, dv, bias, qw, kw, eps, freq, rot_dims, positions, seq_of,
                                                            pages, max_pages, page_size, kc, vc, dt_cache);
   SEQ_LAUNCHED();
   return KB2SEQ_OK;
@@ -614,6 +662,13 @@ KB2SEQ_API int kb2_seq_glu(const void* in, int dt_in, long long ld_in, void* out
                            float alpha, const int* n_tiles, int tile_rows, void* stream) {
   if (!in || !out || rows <= 0 || F <= 0 || ld_in < 2 * F || kind < 0 || kind > 2 || bad_dt(dt_in) || bad_dt(dt_out))
     return failf(KB2SEQ_ERR_VALUE, "glu: bad argument");
+  if (dt_in == 1 && dt_out == 1 && F % 8 == 0 && ld_in % 8 == 0 && !((uintptr_t)in & 15) && !((uintptr_t)out & 15)) {
+    const long long n8 = rows * (F / 8);
+    const unsigned blocks8 = (unsigned)((n8 + 255) / 256 > 148 * 16 ? 148 * 16 : (n8 + 255) / 256);
+    glu_bf16x8_kernel<<<blocks8, 256, 0, (cudaStream_t)stream>>>((const bf16*)in, ld_in, (bf16*)out, rows, F, kind, limit, alpha, n_tiles, tile_rows);
+    SEQ_LAUNCHED();
+    return KB2SEQ_OK;
+  }
   const long long n = rows * F;
   const unsigned blocks = (unsigned)((n + 255) / 256 > 148 * 16 ? 148 * 16 : (n + 255) / 256);
   glu_kernel<<<blocks, 256, 0, (cudaStream_t)stream>>>(in, dt_in, ld_in, out, dt_out, rows, F, kind, limit, alpha, n_tiles, tile_rows);

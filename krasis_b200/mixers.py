@@ -45,11 +45,12 @@ def _core_lib():
     return _core
 
 
-def lin(a: torch.Tensor, w: torch.Tensor, out_dtype=torch.float32) -> torch.Tensor:
-    """a [M, K] @ w [N, K]^T with fp32 accumulation."""
+def lin(a: torch.Tensor, w: torch.Tensor, out_dtype=torch.float32, min_n: int = 256) -> torch.Tensor:
+    """a [M, K] @ w [N, K]^T with fp32 accumulation.  min_n: the narrowest output that still goes to the tcgen05 kernel (its tiles are
+    256 columns wide; a router's few columns are worth it all the same when the step is long)."""
     M, K = a.shape
     N = w.shape[0]
-    if (a.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and M >= 256 and K % 64 == 0 and N % 16 == 0 and N >= 256
+    if (a.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and M >= 256 and K % 64 == 0 and N % 16 == 0 and N >= min_n
             and a.is_contiguous() and w.is_contiguous()):
         core = _core_lib()
         if core:
@@ -402,7 +403,7 @@ class RoutedExperts:
         return y, t["pos"]
 
     def route(self, h: torch.Tensor):
-        return ops.route(lin(h, self.w_router, torch.float32), self.correction, self.top, self.groups, self.keep, self.score, self.renorm,
+        return ops.route(lin(h, self.w_router, torch.float32, min_n=16), self.correction, self.top, self.groups, self.keep, self.score, self.renorm,
                          self.out_scale)
 
     def forward(self, h: torch.Tensor) -> torch.Tensor:
