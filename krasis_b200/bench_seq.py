@@ -145,8 +145,8 @@ def megolorn_config(width=2048, chunk=2048, vocab=32768, experts=62, identity=2,
     """16 query heads x 2 maps x 128 over 2 key/value heads with 256-wide values: the score and value products of the GQA block of
     Qwen3-Next (16 heads x 256 over 2 key/value heads) with the value product doubled.  Every other layer reads the previous layer's
     keys and values and carries routed experts (64 router outputs in 8 groups, 4 kept, top 6) with a shared expert."""
-    att = {"heads": 16, "kv_heads": 2, "dim": 128, "vdim": 256, "diff": 0.6, "scale": 128 ** -0.5, "mask": {"size": chunk},
-           "rot": {"base": 1000000.0, "dims": 64, "scaling": {"factor": 8.0}}}
+    att = {"heads": 16, "kv_heads": 2, "dim": 128, "vdim": 256, "diff": 0.5, "scale": 128 ** -0.5, "mask": {"size": chunk},
+           "rot": {"base": 500000.0, "dims": 64, "scaling": {"factor": 4.0}}}
     moe = {"kind": "moe", "expert": {"ff": expert_ff}, "shared": {"ff": 2 * expert_ff},
            "router": {"experts": experts, "identity": identity, "top": top, "groups": {"count": 8, "keep": 4}}}
     dense = {"kind": "dense", "ff": 4 * width, "limit": 7.0}
@@ -154,7 +154,7 @@ def megolorn_config(width=2048, chunk=2048, vocab=32768, experts=62, identity=2,
     for i in range(2):
         layers.append({"type": "attention", "mixer": dict(att), "mlp": dense})
         layers.append({"type": "attention", "mixer": dict(att, kv_from=2 * i), "mlp": moe})
-    return {"architecture": "Megolorn", "vocab": vocab, "width": width, "embedding": {"scale": 8.0}, "norm": {"eps": 1e-6}, "layers": layers}
+    return {"architecture": "Megolorn", "vocab": vocab, "width": width, "embedding": {"scale": 8.0}, "norm": {"eps": 1e-5}, "layers": layers}
 
 
 def run_megolorn(args, peaks):

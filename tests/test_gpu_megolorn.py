@@ -256,7 +256,7 @@ def test_clamped_swish_and_silu_units(seq):
     close(mlp.forward(h.cuda()).cpu().numpy(), O.silu_glu(h.numpy().astype(np.float64), hw["gate"], hw["up"], hw["down"]), 2e-5, "silu")
 
 
-@pytest.mark.parametrize("E,top,groups,keep", [(12, 3, 4, 2), (10, 2, 2, 1), (7, 7, 1, 1), (64, 5, 8, 3), (9, 1, 3, 3)])
+@pytest.mark.parametrize("E,top,groups,keep", [(12, 3, 4, 2), (15, 2, 3, 1), (7, 7, 1, 1), (64, 5, 8, 3), (9, 1, 3, 3)])
 def test_router_choice_groups_and_weights(seq, E, top, groups, keep):
     T, W = 37, 24
     rw, h = rnd(E, W, seed=E, sd=0.6), rnd(T, W, seed=E + 1)
@@ -387,8 +387,8 @@ def test_pages_and_slots_are_reused(seq):
         s.finish("b")
         lb = s.step([("a", a[10:], list(range(len(a) - 10)))]).cpu().numpy()
         s.finish("a")
-        close(np.concatenate([la[:10], lb], 0), O.forward(raw, w, a), 4e-5, f"round {i}, request a")
-        close(la[10:], O.forward(raw, w, b), 4e-5, f"round {i}, request b")
+        close(np.concatenate([la[:10], lb], 0), O.forward(raw, w, a), 4e-5, f"pass {i}, request a")
+        close(la[10:], O.forward(raw, w, b), 4e-5, f"pass {i}, request b")
         assert s.kv_cache.free_page_count == free0 and s.state_pool.free_slot_count == 2
     with pytest.raises(RuntimeError):
         s.step([("x", toks(60, 50, 1), [])])                    # more pages than the pool has
