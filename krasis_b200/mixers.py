@@ -276,8 +276,12 @@ class MultiMapAttention:
         H, G, M, d, dv, chunk = self.H, self.G, self.M, self.d, self.dv, self.chunk
         first = start // chunk * chunk if chunk else 0
         first = max(first, start - self.window + 1)
-        j = np.arange(first, start + n, dtype=np.int64)
-        rows = torch.from_numpy(np.asarray(pages, dtype=np.int64)[j // page_size] * page_size + j % page_size).to(proj.device, non_blocking=True)
+        key = ("rows_from", i, first, page_size)                  # the layers of a step share the row list of a sequence
+        if key not in tb._key_rows:
+            j = np.arange(first, start + n, dtype=np.int64)
+            host = torch.from_numpy(np.asarray(pages, dtype=np.int64)[j // page_size] * page_size + j % page_size)
+            tb._key_rows[key] = host.to(proj.device, non_blocking=True)
+        rows = tb._key_rows[key]
         k_rows = kc.view(-1, G * M * d).index_select(0, rows)
         v_rows = vc.view(-1, G * dv).index_select(0, rows)
         q = proj[row0:row0 + n, :H * M * d].to(torch.bfloat16).contiguous()
